@@ -1,0 +1,156 @@
+/*
+ * kfa.h - C ABI of the B200-native attention library (libkfa.so).
+ *
+ * Every entry point takes plain pointers, sizes and strides; no C++ or PyTorch
+ * types cross this boundary.  All tensors live in device memory and are
+ * allocated by the caller (outputs and scratch included, except for the one
+ * entry point that says otherwise), so that a caller using a caching allocator
+ * can capture the calls in a CUDA graph.  The library keeps no tensor pointer
+ * between calls.  Kernels are enqueued on the `stream` argument (a
+ * cudaStream_t passed as void*; NULL is the legacy default stream) of the
+ * device that is current on the calling thread.
+ *
+ * Return value: 0 on success, non-zero on failure; the message is available
+ * from kfa_last_error() on the same thread.  Nothing throws or aborts.
+ *
+ * Citations of the form `native.cpp:NNN` or `api.py:NNN` name the file and
+ * line of the reference project (SimpleTuner-io/KohakuFA-CuTe,
+ * src/kohakufa_cute/...) whose host interface the entry point replaces.
+ */
+#ifndef KFA_H
+#define KFA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define KFA_API __attribute__((visibility("default")))
+#else
+#define KFA_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum kfa_dtype { KFA_F16 = 0, KFA_BF16 = 1, KFA_F32 = 2, KFA_BOOL = 3, KFA_I32 = 4 };
+
+/* Non-owning tensor description; strides are in elements.  The reference passes
+ * the same information as non-owning DLTensor views (native.cpp:205-210). */
+typedef struct kfa_tensor {
+    void* data;
+    int32_t dtype; /* enum kfa_dtype */
+    int32_t ndim;  /* <= 6 */
+    int64_t sizes[6];
+    int64_t strides[6];
+} kfa_tensor;
+
+/* Error codes. */
+enum kfa_status {
+    KFA_OK = 0,
+    KFA_INVALID_ARGUMENT = 1, /* shapes, dtypes or strides the operator does not accept */
+    KFA_CUDA_ERROR = 2,       /* a CUDA runtime/driver call failed */
+    KFA_DEVICE_TIMEOUT = 3,   /* a bounded device-side wait ran out (reported by kfa_device_status) */
+    KFA_TOO_LARGE = 4         /* problem exceeds a stated fixed capacity */
+};
+
+/* Library identity: (major << 16) | minor. */
+KFA_API int kfa_version(void);
+
+/* Message of the last failure on the calling thread ("" when none). */
+KFA_API const char* kfa_last_error(void);
+
+/*
+ * Attention forward.  Replaces the module function `forward` of the reference's
+ * host launcher (native.cpp:1034-1037, forward_canonical native.cpp:294-314).
+ *
+ *   q [B,Hq,Sq,D], k,v [B,Hkv,Sk,D]  fp16 or bf16, any strides, Hq % Hkv == 0, 1 <= D <= 512
+ *   mask     NULL, or a bool tensor already expanded to [B,Hq,Sq,Sk] (stride 0 on broadcast axes)
+ *   out      [B,Hq,Sq,D] same dtype as q (the caller gives it q's strides)
+ *   maximum  [B,Hq,Sq] f32: row maximum of the unscaled scores times sign(scale)
+ *   logsum   [B,Hq,Sq] f32: log2 of the softmax normaliser relative to `maximum`
+ *   blocks   int32 tile table [Bm,Hm,ceil(Sq/64) or 1,ceil(Sk/64) or 1] written when mask != NULL
+ *            (extent 1 on the mask's stride-0 axes); NULL when mask == NULL
+ * A row with no visible key yields out = 0, maximum = -inf, logsum = 0.
+ */
+KFA_API int kfa_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
+                kfa_tensor* out, kfa_tensor* maximum, kfa_tensor* logsum, kfa_tensor* blocks, float scale,
+                int causal, void* stream);
+
+/* Bytes of scratch kfa_backward needs for these shapes (native.cpp:341-354 sizes the
+ * same buffers: delta and its base). */
+KFA_API size_t kfa_backward_workspace_bytes(const kfa_tensor* q, const kfa_tensor* k);
+
+/*
+ * Attention backward.  Replaces `backward` (native.cpp:1038-1042, 341-358).
+ * Reads the forward's saved out/maximum/logsum/blocks; writes dq (like q) and dk, dv (like k, v).
+ * `workspace` must hold kfa_backward_workspace_bytes() bytes, 256-byte aligned.
+ */
+KFA_API int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
+                 const kfa_tensor* out, const kfa_tensor* maximum, const kfa_tensor* logsum,
+                 const kfa_tensor* dout, const kfa_tensor* blocks, kfa_tensor* dq, kfa_tensor* dk,
+                 kfa_tensor* dv, void* workspace, size_t workspace_bytes, float scale, int causal,
+                 void* stream);
+
+/*
+ * Key centering: centered = round(f32(k) - mean over the sequence axis of f32(k)) per
+ * (batch, head, channel).  Replaces the PyTorch expression at api.py:100-103.  The same
+ * entry point computes the gradient projection (apply it to the centred-key gradient).
+ * `workspace` holds B*H*D floats.
+ */
+KFA_API size_t kfa_center_keys_workspace_bytes(const kfa_tensor* k);
+KFA_API int kfa_center_keys(const kfa_tensor* k, kfa_tensor* centered, void* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/*
+ * Neighbourhood (shifted-window) attention, head dim 64, equal Q/K/V shapes
+ * [B,H,prod(spatial),64].  Replaces `neighborhood_forward` (native.cpp:1043-1054) and the
+ * Python-side backward launch (neighborhood_kernels.py:408-411).  `nd` is 2 or 3.
+ * The 3-D forward uses the two-term probability product.
+ */
+KFA_API int kfa_neighborhood_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, kfa_tensor* out,
+                             kfa_tensor* maximum, kfa_tensor* logsum, const int64_t* spatial, int nd,
+                             const int64_t* window, float scale, void* stream);
+KFA_API size_t kfa_neighborhood_backward_workspace_bytes(const kfa_tensor* q);
+KFA_API int kfa_neighborhood_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v,
+                              const kfa_tensor* out, const kfa_tensor* maximum, const kfa_tensor* logsum,
+                              const kfa_tensor* dout, kfa_tensor* dq, kfa_tensor* dk, kfa_tensor* dv,
+                              void* workspace, size_t workspace_bytes, const int64_t* spatial, int nd,
+                              const int64_t* window, float scale, void* stream);
+
+/*
+ * Merge step of ring context parallelism: folds the partial result of attending to one
+ * more key/value block into a running result.  Each side is (out, maximum, logsum) as
+ * kfa_forward returns them; `acc_*` are updated in place.  The arithmetic is the
+ * (max, sum) merge of the reference's split forward (split_forward.py:219-245).
+ *   acc_out/part_out [B,H,S,D] (acc is f32, part is the 16-bit type), stats [B,H,S] f32
+ */
+KFA_API int kfa_merge_partial(kfa_tensor* acc_out, kfa_tensor* acc_maximum, kfa_tensor* acc_logsum,
+                      const kfa_tensor* part_out, const kfa_tensor* part_maximum,
+                      const kfa_tensor* part_logsum, float scale, void* stream);
+
+/* Number of kernel variants configured so far / forget them.  Replace `cache_size`
+ * and `clear_cache` (native.cpp:1055-1065). */
+KFA_API int kfa_cache_size(void);
+KFA_API void kfa_clear_cache(void);
+
+/* Kernels launched by this library since load (all threads) - observability only. */
+KFA_API uint64_t kfa_launch_count(void);
+
+/*
+ * Device-side status: 0 when no kernel reported a problem, otherwise the code a bounded
+ * wait stored when it gave up.  Reading does not synchronise; call after the stream is
+ * idle.  `reset` != 0 clears it.
+ */
+KFA_API int kfa_device_status(int reset);
+
+/* Which kernel family kfa_forward / kfa_backward would select for these operands:
+ * 0 = general kernels, 1 = tcgen05 tensor-memory pipeline.  (The reference exposes its
+ * selection through kernels.kernel_configuration, kernels.py:2593-2637.) */
+KFA_API int kfa_selected_family(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v,
+                        const kfa_tensor* mask, int causal, int backward);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KFA_H */

@@ -1,0 +1,439 @@
+// C ABI of libkfa.so: argument validation, kernel-family selection and launches.
+// Declarations and the reference interfaces they replace are in include/kfa.h.
+#include "../../include/kfa.h"
+#include "kfa_common.cuh"
+#include "launchers.h"
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+namespace {
+
+thread_local char g_error[512] = "";
+std::atomic<uint64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+int cuda_fail(cudaError_t e, const char* what) {
+    return fail(KFA_CUDA_ERROR, "%s: %s", what, cudaGetErrorString(e));
+}
+
+// Per-device status word in mapped host memory: kernels write it only when a
+// bounded wait gives up; the host reads it without synchronising.
+constexpr int kMaxDevices = 64;
+int* g_status_host[kMaxDevices] = {};
+int* g_status_dev[kMaxDevices] = {};
+std::mutex g_status_mutex;
+
+int* status_word(int* err) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        *err = cuda_fail(e, "cudaGetDevice");
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    if (!g_status_dev[dev]) {
+        int* host = nullptr;
+        e = cudaHostAlloc(reinterpret_cast<void**>(&host), 64, cudaHostAllocMapped | cudaHostAllocPortable);
+        if (e != cudaSuccess) {
+            *err = cuda_fail(e, "cudaHostAlloc(status)");
+            return nullptr;
+        }
+        std::memset(host, 0, 64);
+        int* devp = nullptr;
+        e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&devp), host, 0);
+        if (e != cudaSuccess) {
+            *err = cuda_fail(e, "cudaHostGetDevicePointer(status)");
+            return nullptr;
+        }
+        g_status_host[dev] = host;
+        g_status_dev[dev] = devp;
+    }
+    return g_status_dev[dev];
+}
+
+bool is_half_type(const kfa_tensor* t) { return t->dtype == KFA_F16 || t->dtype == KFA_BF16; }
+
+void copy4(int64_t* dst, const int64_t* src) {
+    for (int i = 0; i < 4; ++i) dst[i] = src[i];
+}
+
+bool contiguous3(const kfa_tensor* t, int64_t b, int64_t h, int64_t s) {
+    return t && t->data && t->dtype == KFA_F32 && t->ndim == 3 && t->sizes[0] == b && t->sizes[1] == h &&
+           t->sizes[2] == s && t->strides[2] == 1 && t->strides[1] == s && t->strides[0] == h * s;
+}
+
+bool same_shape(const kfa_tensor* a, const kfa_tensor* b) {
+    if (a->ndim != b->ndim) return false;
+    for (int i = 0; i < a->ndim; ++i)
+        if (a->sizes[i] != b->sizes[i]) return false;
+    return true;
+}
+
+// Shared checks for q/k/v (messages mirror the reference's validation wording: api.py:76-97).
+int check_qkv(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v) {
+    if (!q || !k || !v || !q->data || !k->data || !v->data) return fail(KFA_INVALID_ARGUMENT, "null Q/K/V");
+    if (q->ndim != 4 || k->ndim != 4 || v->ndim != 4)
+        return fail(KFA_INVALID_ARGUMENT, "attention requires 4D [batch, heads, sequence, dim] Q/K/V");
+    if (!is_half_type(q) || k->dtype != q->dtype || v->dtype != q->dtype)
+        return fail(KFA_INVALID_ARGUMENT, "attention requires matching FP16/BF16 Q/K/V; FP32 attention is unsupported");
+    for (int i = 0; i < 4; ++i)
+        if (q->sizes[i] <= 0 || k->sizes[i] <= 0)
+            return fail(KFA_INVALID_ARGUMENT, "attention requires nonempty Q/K/V");
+    if (!same_shape(k, v) || q->sizes[0] != k->sizes[0] || q->sizes[3] != k->sizes[3])
+        return fail(KFA_INVALID_ARGUMENT, "attention requires matching batch/head dimensions and equal K/V shapes");
+    if (q->sizes[1] % k->sizes[1] != 0 || q->sizes[3] > 512)
+        return fail(KFA_INVALID_ARGUMENT, "attention requires head dimensions 1..512 and query heads divisible by K/V heads");
+    if (q->sizes[2] > INT32_MAX || k->sizes[2] > INT32_MAX || q->sizes[0] * q->sizes[1] > INT32_MAX)
+        return fail(KFA_TOO_LARGE, "sequence length or batch*heads exceeds 2^31-1");
+    return 0;
+}
+
+int fill_common(kfa::AttnParams& p, const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v,
+                const kfa_tensor* mask, float scale, int causal) {
+    std::memset(&p, 0, sizeof(p));
+    p.q = q->data;
+    p.k = k->data;
+    p.v = v->data;
+    copy4(p.qs, q->strides);
+    copy4(p.ks, k->strides);
+    copy4(p.vs, v->strides);
+    p.B = (int)q->sizes[0];
+    p.Hq = (int)q->sizes[1];
+    p.Hkv = (int)k->sizes[1];
+    p.Sq = (int)q->sizes[2];
+    p.Sk = (int)k->sizes[2];
+    p.D = (int)q->sizes[3];
+    p.group = p.Hq / p.Hkv;
+    p.scale = scale;
+    p.causal = causal ? 1 : 0;
+    if (mask) {
+        if (mask->dtype != KFA_BOOL || mask->ndim != 4 || !mask->data)
+            return fail(KFA_INVALID_ARGUMENT, "attention requires a boolean mask expanded to [B,Hq,Sq,Sk]");
+        if (mask->sizes[0] != q->sizes[0] || mask->sizes[1] != q->sizes[1] || mask->sizes[2] != q->sizes[2] ||
+            mask->sizes[3] != k->sizes[2])
+            return fail(KFA_INVALID_ARGUMENT, "mask shape does not match [B,Hq,Sq,Sk]");
+        p.mask = static_cast<const uint8_t*>(mask->data);
+        copy4(p.ms, mask->strides);
+        p.has_mask = 1;
+    }
+    int err = 0;
+    p.status = status_word(&err);
+    return err;
+}
+
+// Extents of the tile table for this mask (extent 1 on stride-0 axes).
+void block_extents(const kfa::AttnParams& p, int64_t (&n)[4]) {
+    n[0] = p.ms[0] == 0 ? 1 : p.B;
+    n[1] = p.ms[1] == 0 ? 1 : p.Hq;
+    n[2] = p.ms[2] == 0 ? 1 : (p.Sq + 63) / 64;
+    n[3] = p.ms[3] == 0 ? 1 : (p.Sk + 63) / 64;
+}
+
+int bind_blocks(kfa::AttnParams& p, const kfa_tensor* blocks) {
+    if (!p.has_mask) return 0;
+    int64_t n[4];
+    block_extents(p, n);
+    if (!blocks || !blocks->data || blocks->dtype != KFA_I32 || blocks->ndim != 4)
+        return fail(KFA_INVALID_ARGUMENT, "masked attention requires an int32 4-D tile table");
+    for (int i = 0; i < 4; ++i)
+        if (blocks->sizes[i] != n[i])
+            return fail(KFA_INVALID_ARGUMENT, "tile table extent %d is %lld, expected %lld", i,
+                        (long long)blocks->sizes[i], (long long)n[i]);
+    // The table is dense over its own extents; collapsed axes get stride 0 for lookups.
+    if (blocks->strides[3] != 1 || blocks->strides[2] != n[3] || blocks->strides[1] != n[2] * n[3] ||
+        blocks->strides[0] != n[1] * n[2] * n[3])
+        return fail(KFA_INVALID_ARGUMENT, "tile table must be contiguous");
+    p.blocks = static_cast<int32_t*>(blocks->data);
+    p.bs[0] = n[0] == 1 ? 0 : blocks->strides[0];
+    p.bs[1] = n[1] == 1 ? 0 : blocks->strides[1];
+    p.bs[2] = n[2] == 1 ? 0 : blocks->strides[2];
+    p.bs[3] = n[3] == 1 ? 0 : blocks->strides[3];
+    return 0;
+}
+
+int check_like(const kfa_tensor* t, const kfa_tensor* like, const char* name) {
+    if (!t || !t->data || t->dtype != like->dtype || !same_shape(t, like))
+        return fail(KFA_INVALID_ARGUMENT, "%s must match the shape and dtype of its source tensor", name);
+    return 0;
+}
+
+int geometry(kfa::AttnParams& p, const int64_t* spatial, int nd, const int64_t* window) {
+    if ((nd != 2 && nd != 3) || !spatial || !window)
+        return fail(KFA_INVALID_ARGUMENT, "spatial_shape must contain two or three positive integers");
+    int64_t tokens = 1;
+    for (int i = 0; i < 3; ++i) {
+        const int src = i - (3 - nd);
+        const int64_t e = src < 0 ? 1 : spatial[src], w = src < 0 ? 1 : window[src];
+        if (e <= 0 || e > INT32_MAX) return fail(KFA_INVALID_ARGUMENT, "spatial_shape must contain positive integers");
+        if (w <= 0 || w > e)
+            return fail(KFA_INVALID_ARGUMENT, "window_size must contain positive integers no larger than spatial_shape");
+        p.ext[i] = (int)e;
+        p.win[i] = (int)w;
+        tokens *= e;
+    }
+    if (tokens != p.Sq || p.Sq != p.Sk || p.D != 64 || p.Hq != p.Hkv)
+        return fail(KFA_INVALID_ARGUMENT,
+                    "neighborhood attention requires matching [B, heads, prod(spatial_shape), 64] Q/K/V");
+    p.nd = nd;
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int kfa_version(void) { return (0 << 16) | 1; }
+
+const char* kfa_last_error(void) { return g_error; }
+
+uint64_t kfa_launch_count(void) { return g_launches.load(); }
+
+int kfa_cache_size(void) { return kfa::pipeline_configured_variants(); }
+
+void kfa_clear_cache(void) { kfa::pipeline_forget_variants(); }
+
+int kfa_device_status(int reset) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    if (!g_status_host[dev]) return 0;
+    const int value = *reinterpret_cast<volatile int*>(g_status_host[dev]);
+    if (reset) *reinterpret_cast<volatile int*>(g_status_host[dev]) = 0;
+    return value;
+}
+
+int kfa_selected_family(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
+                        int causal, int backward) {
+    if (check_qkv(q, k, v)) return -1;
+    kfa::AttnParams p;
+    if (fill_common(p, q, k, v, mask, 1.f, causal)) return -1;
+    // Output strides follow the inputs (the caller allocates them like q/k/v).
+    p.out = const_cast<void*>(q->data);
+    copy4(p.os, q->strides);
+    p.dout = q->data;
+    copy4(p.gs, q->strides);
+    p.dq = const_cast<void*>(q->data);
+    copy4(p.dqs, q->strides);
+    p.dk = const_cast<void*>(k->data);
+    copy4(p.dks, k->strides);
+    p.dv = const_cast<void*>(v->data);
+    copy4(p.dvs, v->strides);
+    const bool bf16 = q->dtype == KFA_BF16;
+    return backward ? (kfa::pipeline_backward_supported(p, bf16) ? 1 : 0)
+                    : (kfa::pipeline_forward_supported(p, bf16) ? 1 : 0);
+}
+
+int kfa_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
+                kfa_tensor* out, kfa_tensor* maximum, kfa_tensor* logsum, kfa_tensor* blocks, float scale,
+                int causal, void* stream) {
+    if (int e = check_qkv(q, k, v)) return e;
+    kfa::AttnParams p;
+    if (int e = fill_common(p, q, k, v, mask, scale, causal)) return e;
+    if (int e = check_like(out, q, "out")) return e;
+    if (!contiguous3(maximum, p.B, p.Hq, p.Sq) || !contiguous3(logsum, p.B, p.Hq, p.Sq))
+        return fail(KFA_INVALID_ARGUMENT, "maximum/logsum must be contiguous float32 [B,Hq,Sq]");
+    if (int e = bind_blocks(p, blocks)) return e;
+    p.out = out->data;
+    copy4(p.os, out->strides);
+    p.maximum = static_cast<float*>(maximum->data);
+    p.logsum = static_cast<float*>(logsum->data);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool bf16 = q->dtype == KFA_BF16;
+    cudaError_t ce;
+    if (p.has_mask) {
+        int64_t n[4];
+        block_extents(p, n);
+        ce = kfa::launch_pack_mask(p, (int)n[0], (int)n[1], (int)n[2], (int)n[3], st);
+        if (ce != cudaSuccess) return cuda_fail(ce, "pack_mask launch");
+        g_launches += 1;
+    }
+    if (kfa::pipeline_forward_supported(p, bf16)) {
+        ce = kfa::launch_pipeline_forward(p, bf16, st);
+        if (ce != cudaSuccess) return cuda_fail(ce, "pipeline forward launch");
+    } else {
+        ce = kfa::launch_general_forward(p, bf16, st);
+        if (ce != cudaSuccess) return cuda_fail(ce, "general forward launch");
+    }
+    g_launches += 1;
+    return 0;
+}
+
+size_t kfa_backward_workspace_bytes(const kfa_tensor* q, const kfa_tensor* k) {
+    (void)k;
+    if (!q || q->ndim != 4) return 0;
+    const size_t rows = (size_t)q->sizes[0] * q->sizes[1] * q->sizes[2];
+    return ((rows * sizeof(float) + 255) / 256) * 256;
+}
+
+int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
+                 const kfa_tensor* out, const kfa_tensor* maximum, const kfa_tensor* logsum, const kfa_tensor* dout,
+                 const kfa_tensor* blocks, kfa_tensor* dq, kfa_tensor* dk, kfa_tensor* dv, void* workspace,
+                 size_t workspace_bytes, float scale, int causal, void* stream) {
+    if (int e = check_qkv(q, k, v)) return e;
+    kfa::AttnParams p;
+    if (int e = fill_common(p, q, k, v, mask, scale, causal)) return e;
+    if (int e = check_like(out, q, "out")) return e;
+    if (int e = check_like(dout, q, "dout")) return e;
+    if (int e = check_like(dq, q, "dq")) return e;
+    if (int e = check_like(dk, k, "dk")) return e;
+    if (int e = check_like(dv, v, "dv")) return e;
+    if (!contiguous3(maximum, p.B, p.Hq, p.Sq) || !contiguous3(logsum, p.B, p.Hq, p.Sq))
+        return fail(KFA_INVALID_ARGUMENT, "maximum/logsum must be contiguous float32 [B,Hq,Sq]");
+    if (int e = bind_blocks(p, blocks)) return e;
+    if (!workspace || workspace_bytes < kfa_backward_workspace_bytes(q, k) ||
+        reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+        return fail(KFA_INVALID_ARGUMENT, "backward workspace too small or not 256-byte aligned");
+    p.out = const_cast<void*>(out->data);
+    copy4(p.os, out->strides);
+    p.maximum = static_cast<float*>(maximum->data);
+    p.logsum = static_cast<float*>(logsum->data);
+    p.dout = dout->data;
+    copy4(p.gs, dout->strides);
+    p.delta = static_cast<float*>(workspace);
+    p.dq = dq->data;
+    copy4(p.dqs, dq->strides);
+    p.dk = dk->data;
+    copy4(p.dks, dk->strides);
+    p.dv = dv->data;
+    copy4(p.dvs, dv->strides);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool bf16 = q->dtype == KFA_BF16;
+    cudaError_t ce = kfa::launch_output_delta(p, bf16, st);
+    if (ce != cudaSuccess) return cuda_fail(ce, "output_delta launch");
+    if (kfa::pipeline_backward_supported(p, bf16)) {
+        ce = kfa::launch_pipeline_backward(p, bf16, st);
+        if (ce != cudaSuccess) return cuda_fail(ce, "pipeline backward launch");
+    } else {
+        ce = kfa::launch_general_backward(p, bf16, st);
+        if (ce != cudaSuccess) return cuda_fail(ce, "general backward launch");
+    }
+    g_launches += 3;
+    return 0;
+}
+
+size_t kfa_center_keys_workspace_bytes(const kfa_tensor* k) {
+    if (!k || k->ndim != 4) return 0;
+    return ((size_t)k->sizes[0] * k->sizes[1] * k->sizes[3] * sizeof(float) + 255) / 256 * 256;
+}
+
+int kfa_center_keys(const kfa_tensor* k, kfa_tensor* centered, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!k || !k->data || k->ndim != 4 || !is_half_type(k))
+        return fail(KFA_INVALID_ARGUMENT, "center_keys requires a 4D FP16/BF16 tensor");
+    if (int e = check_like(centered, k, "centered")) return e;
+    if (!workspace || workspace_bytes < kfa_center_keys_workspace_bytes(k))
+        return fail(KFA_INVALID_ARGUMENT, "center_keys workspace too small");
+    for (int i = 0; i < 4; ++i)
+        if (k->sizes[i] <= 0 || k->sizes[i] > INT32_MAX) return fail(KFA_INVALID_ARGUMENT, "center_keys: bad extent");
+    if (k->sizes[0] * k->sizes[1] > 65535) return fail(KFA_TOO_LARGE, "center_keys: batch*heads exceeds 65535");
+    cudaError_t ce = kfa::launch_center_keys(k->data, centered->data, static_cast<float*>(workspace),
+                                             k->dtype == KFA_BF16, (int)k->sizes[0], (int)k->sizes[1],
+                                             (int)k->sizes[2], (int)k->sizes[3], k->strides, centered->strides,
+                                             static_cast<cudaStream_t>(stream));
+    if (ce != cudaSuccess) return cuda_fail(ce, "center_keys launch");
+    g_launches += 2;
+    return 0;
+}
+
+int kfa_neighborhood_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, kfa_tensor* out,
+                             kfa_tensor* maximum, kfa_tensor* logsum, const int64_t* spatial, int nd,
+                             const int64_t* window, float scale, void* stream) {
+    if (int e = check_qkv(q, k, v)) return e;
+    kfa::AttnParams p;
+    if (int e = fill_common(p, q, k, v, nullptr, scale, 0)) return e;
+    if (int e = geometry(p, spatial, nd, window)) return e;
+    if (int e = check_like(out, q, "out")) return e;
+    if (!contiguous3(maximum, p.B, p.Hq, p.Sq) || !contiguous3(logsum, p.B, p.Hq, p.Sq))
+        return fail(KFA_INVALID_ARGUMENT, "maximum/logsum must be contiguous float32 [B,H,S]");
+    p.out = out->data;
+    copy4(p.os, out->strides);
+    p.maximum = static_cast<float*>(maximum->data);
+    p.logsum = static_cast<float*>(logsum->data);
+    p.two_term = nd == 3 ? 1 : 0;
+    cudaError_t ce = kfa::launch_neighborhood_forward(p, q->dtype == KFA_BF16, static_cast<cudaStream_t>(stream));
+    if (ce != cudaSuccess) return cuda_fail(ce, "neighborhood forward launch");
+    g_launches += 1;
+    return 0;
+}
+
+size_t kfa_neighborhood_backward_workspace_bytes(const kfa_tensor* q) {
+    if (!q || q->ndim != 4) return 0;
+    const size_t rows = (size_t)q->sizes[0] * q->sizes[1] * q->sizes[2];
+    return 2 * (((rows * sizeof(float) + 255) / 256) * 256);
+}
+
+int kfa_neighborhood_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* out,
+                              const kfa_tensor* maximum, const kfa_tensor* logsum, const kfa_tensor* dout,
+                              kfa_tensor* dq, kfa_tensor* dk, kfa_tensor* dv, void* workspace, size_t workspace_bytes,
+                              const int64_t* spatial, int nd, const int64_t* window, float scale, void* stream) {
+    if (int e = check_qkv(q, k, v)) return e;
+    kfa::AttnParams p;
+    if (int e = fill_common(p, q, k, v, nullptr, scale, 0)) return e;
+    if (int e = geometry(p, spatial, nd, window)) return e;
+    if (int e = check_like(out, q, "out")) return e;
+    if (int e = check_like(dout, q, "dout")) return e;
+    if (int e = check_like(dq, q, "dq")) return e;
+    if (int e = check_like(dk, k, "dk")) return e;
+    if (int e = check_like(dv, v, "dv")) return e;
+    if (!contiguous3(maximum, p.B, p.Hq, p.Sq) || !contiguous3(logsum, p.B, p.Hq, p.Sq))
+        return fail(KFA_INVALID_ARGUMENT, "maximum/logsum must be contiguous float32 [B,H,S]");
+    const size_t need = kfa_neighborhood_backward_workspace_bytes(q);
+    if (!workspace || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+        return fail(KFA_INVALID_ARGUMENT, "neighborhood backward workspace too small or not 256-byte aligned");
+    p.out = const_cast<void*>(out->data);
+    copy4(p.os, out->strides);
+    p.maximum = static_cast<float*>(maximum->data);
+    p.logsum = static_cast<float*>(logsum->data);
+    p.dout = dout->data;
+    copy4(p.gs, dout->strides);
+    p.delta = static_cast<float*>(workspace);
+    p.aux = reinterpret_cast<float*>(static_cast<char*>(workspace) + need / 2);
+    p.dq = dq->data;
+    copy4(p.dqs, dq->strides);
+    p.dk = dk->data;
+    copy4(p.dks, dk->strides);
+    p.dv = dv->data;
+    copy4(p.dvs, dv->strides);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool bf16 = q->dtype == KFA_BF16;
+    cudaError_t ce = kfa::launch_output_delta(p, bf16, st);
+    if (ce != cudaSuccess) return cuda_fail(ce, "output_delta launch");
+    ce = kfa::launch_neighborhood_backward(p, bf16, st);
+    if (ce != cudaSuccess) return cuda_fail(ce, "neighborhood backward launch");
+    g_launches += 3;
+    return 0;
+}
+
+int kfa_merge_partial(kfa_tensor* acc_out, kfa_tensor* acc_maximum, kfa_tensor* acc_logsum, const kfa_tensor* part_out,
+                      const kfa_tensor* part_maximum, const kfa_tensor* part_logsum, float scale, void* stream) {
+    if (!acc_out || !part_out || acc_out->ndim != 4 || part_out->ndim != 4 || !same_shape(acc_out, part_out))
+        return fail(KFA_INVALID_ARGUMENT, "merge requires matching 4D outputs");
+    if (acc_out->dtype != KFA_F32 || !is_half_type(part_out))
+        return fail(KFA_INVALID_ARGUMENT, "merge requires an FP32 running output and an FP16/BF16 partial output");
+    const int64_t B = acc_out->sizes[0], H = acc_out->sizes[1], S = acc_out->sizes[2], D = acc_out->sizes[3];
+    if (acc_out->strides[3] != 1 || acc_out->strides[2] != D || acc_out->strides[1] != S * D ||
+        acc_out->strides[0] != H * S * D)
+        return fail(KFA_INVALID_ARGUMENT, "merge requires a contiguous running output");
+    if (!contiguous3(acc_maximum, B, H, S) || !contiguous3(acc_logsum, B, H, S) ||
+        !contiguous3(part_maximum, B, H, S) || !contiguous3(part_logsum, B, H, S))
+        return fail(KFA_INVALID_ARGUMENT, "merge statistics must be contiguous float32 [B,H,S]");
+    cudaError_t ce = kfa::launch_merge_partial(
+        static_cast<float*>(acc_out->data), static_cast<float*>(acc_maximum->data),
+        static_cast<float*>(acc_logsum->data), part_out->data, static_cast<const float*>(part_maximum->data),
+        static_cast<const float*>(part_logsum->data), part_out->dtype == KFA_BF16, (int)B, (int)H, (int)S, (int)D,
+        part_out->strides, scale, static_cast<cudaStream_t>(stream));
+    if (ce != cudaSuccess) return cuda_fail(ce, "merge launch");
+    g_launches += 1;
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,92 @@
+// Shared parameter blocks and small device helpers for all attention kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <math.h>
+
+namespace kfa {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// Operands of one attention call.  Strides are in elements; index order is
+// (batch, head, sequence, channel).  Unused pointers are null.
+struct AttnParams {
+    const void* q;
+    const void* k;
+    const void* v;
+    const uint8_t* mask;  // bool, expanded to [B,Hq,Sq,Sk] with stride 0 on broadcast axes
+    void* out;            // forward output (written) or saved output (read by backward)
+    float* maximum;       // [B,Hq,Sq]
+    float* logsum;        // [B,Hq,Sq]
+    const void* dout;
+    float* delta;         // [B,Hq,Sq] scratch: sum_d O * dO
+    float* aux;           // [B,Hq,Sq] scratch: neighbourhood correction t
+    void* dq;
+    void* dk;
+    void* dv;
+    int32_t* blocks;      // 64x64 mask tile states
+    int64_t qs[4], ks[4], vs[4], os[4], ms[4], gs[4], dqs[4], dks[4], dvs[4];
+    int64_t bs[4];        // strides of `blocks` (0 on collapsed axes)
+    int B, Hq, Hkv, Sq, Sk, D, group;
+    float scale;
+    int causal;
+    int has_mask;
+    // neighbourhood geometry (nd = 0 for ordinary attention); axis order slowest..fastest,
+    // 2-D grids use ext[0] = 1, win[0] = 1.
+    int nd;
+    int ext[3];
+    int win[3];
+    int two_term;
+    int* status;  // device-visible status word (mapped host memory)
+};
+
+template <typename T>
+__device__ __forceinline__ float to_float(T x);
+template <>
+__device__ __forceinline__ float to_float<__half>(__half x) { return __half2float(x); }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float x);
+template <>
+__device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// One round trip through the 16-bit type.
+template <typename T>
+__device__ __forceinline__ float round_low(float x) { return to_float<T>(from_float<T>(x)); }
+
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ float warp_max(float x) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+    return x;
+}
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    return x;
+}
+
+// Window start of a neighbourhood query on one axis: clamp(p - w/2, 0, e - w).
+__host__ __device__ __forceinline__ int na_start(int p, int e, int w) {
+    int s = p - w / 2;
+    s = s < 0 ? 0 : s;
+    return s > e - w ? e - w : s;
+}
+// Inclusive range of query coordinates whose window holds key coordinate `c`.
+__host__ __device__ __forceinline__ void na_inverse(int c, int e, int w, int& lo, int& hi) {
+    lo = (c - w + 1 <= 0) ? 0 : c - w + 1 + w / 2;
+    hi = (c >= e - w) ? e - 1 : c + w / 2;
+}
+
+}  // namespace kfa

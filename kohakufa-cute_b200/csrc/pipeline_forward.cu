@@ -1,0 +1,431 @@
+// Attention forward on the Blackwell tensor-memory pipeline (tcgen05 + TMEM + TMA),
+// head dim 64 or 128, FP16/BF16, causal and/or key-padding masks, grouped-query heads.
+//
+// One CTA owns 256 query rows of one (batch, query head) as two 128-row tiles and walks
+// the 128-key tiles they can see.  Warp roles (320 threads):
+//   warps 0-3  softmax of query tile 0   (thread i <-> TMEM lane i <-> query row i)
+//   warps 4-7  softmax of query tile 1
+//   warp  8    issues every tcgen05.mma (one elected lane), owns the TMEM allocation
+//   warp  9    TMA loader (one elected lane); warps 10-11 idle (they complete the warpgroup so
+//              that registers can be moved from it to the softmax warpgroups)
+// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 columns each.  The 16-bit
+// probabilities overwrite the first 64 columns of their score tile and feed the second
+// product straight from tensor memory.  While one tile's softmax runs, the tensor core
+// works on the other tile, and K/V tiles are shared by both.
+//
+// Arithmetic (reference behaviour: src/kohakufa_cute/blackwell_pipeline.py:141-209,
+// 423-439 and kernels.py:1286-1333 of the reference project): scores are used unscaled,
+// the row maximum is subtracted before the multiplication by |scale|*log2e, the
+// normaliser sums unrounded probabilities while the product uses probabilities rounded
+// once to the input type, and the saved statistics are the exact unscaled row maximum
+// and log2 of the normaliser relative to it.  The accumulator is re-based only when
+// the running maximum has grown by more than 2^8 in probability terms; the statistics
+// are corrected for the difference at the end, so they do not depend on that choice.
+#include "kfa_common.cuh"
+#include "launchers.h"
+#include "sm100_ptx.cuh"
+#include "tensor_map.h"
+
+#include <atomic>
+#include <type_traits>
+
+namespace kfa {
+namespace {
+
+constexpr int kTileQ = 128;
+constexpr int kTileK = 128;
+constexpr int kThreads = 384;  // three warpgroups: softmax 0, softmax 1, (MMA, loader, 2 idle warps)
+constexpr float kRebase = 8.0f;  // re-base the accumulator when the maximum grows by > 2^8
+
+template <int D>
+struct FwdCfg {
+    static constexpr int kChunks = D / 64;                 // 64-channel TMA boxes per tile
+    static constexpr int kTileBytes = kTileK * D * 2;      // one Q, K or V tile
+    static constexpr int kStages = D == 128 ? 4 : 6;       // K/V ring slots
+    static constexpr int kSmemBytes = 2 * kTileBytes + kStages * kTileBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct FwdMaps {
+    CUtensorMap q, k, v;
+};
+
+struct Shared {
+    uint64_t q_full;
+    uint64_t kv_full[6];
+    uint64_t kv_empty[6];
+    uint64_t s_ready[2];
+    uint64_t p_ready[2];
+    uint32_t tmem_base;
+    int abort_word;
+};
+
+// Combined state of key tile j (128 keys) from the 64-key table entries: 0 hidden, 2 visible, 1 mixed.
+__device__ __forceinline__ int key_tile_state(const AttnParams& p, int b, int h, int j) {
+    if (!p.has_mask) return 2;
+    const int nk64 = (p.Sk + 63) >> 6;
+    const int32_t* base = p.blocks + (int64_t)b * p.bs[0] + (int64_t)h * p.bs[1];
+    const int s0 = base[(int64_t)(2 * j) * p.bs[3]];
+    const int s1 = (2 * j + 1 < nk64) ? base[(int64_t)(2 * j + 1) * p.bs[3]] : s0;
+    if (s0 == 0 && s1 == 0) return 0;
+    if (s0 == 2 && s1 == 2) return 2;
+    return 1;
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_constant__ FwdMaps maps, AttnParams p) {
+    using Cfg = FwdCfg<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = smem;                          // two query tiles
+    uint8_t* sKV = smem + 2 * Cfg::kTileBytes;   // ring of K/V tiles
+    Shared& sh = *reinterpret_cast<Shared*>(sKV + Cfg::kStages * Cfg::kTileBytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nblk = (p.Sq + 2 * kTileQ - 1) / (2 * kTileQ);
+    const int qblk = nblk - 1 - (int)(blockIdx.x % nblk);  // heavy (late) causal blocks first
+    const int64_t bh = blockIdx.x / nblk;
+    const int h = (int)(bh % p.Hq), b = (int)(bh / p.Hq);
+    const int kvh = h / p.group;
+    const int q0 = qblk * 2 * kTileQ;
+
+    // key tiles each query tile may see
+    int n_t[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int row_lo = q0 + t * kTileQ;
+        if (row_lo >= p.Sq) {
+            n_t[t] = 0;
+        } else {
+            const int row_hi = min(p.Sq, row_lo + kTileQ);
+            const int k_hi = p.causal ? min(p.Sk, row_hi) : p.Sk;
+            n_t[t] = (k_hi + kTileK - 1) / kTileK;
+        }
+    }
+    const int n_max = max(n_t[0], n_t[1]);
+
+    if (threadIdx.x == 0) {
+        sh.abort_word = 0;
+        mbar_init(&sh.q_full, 1);
+        for (int i = 0; i < Cfg::kStages; ++i) {
+            mbar_init(&sh.kv_full[i], 1);
+            mbar_init(&sh.kv_empty[i], 1);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&sh.s_ready[t], 1);
+            mbar_init(&sh.p_ready[t], kTileQ);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 8) {
+        tmem_alloc(&sh.tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    volatile int* abort_word = &sh.abort_word;
+
+    if (warp >= 8) {
+      reg_dealloc<40>();
+      if (warp == 9) {
+        // ------------------------------------------------------------ loader
+        if (lane == 0) {
+            tma_prefetch_desc(&maps.q);
+            tma_prefetch_desc(&maps.k);
+            tma_prefetch_desc(&maps.v);
+            const int active = (n_t[0] > 0 ? 1 : 0) + (n_t[1] > 0 ? 1 : 0);
+            mbar_expect_tx(&sh.q_full, active * Cfg::kTileBytes);
+            for (int t = 0; t < 2; ++t)
+                if (n_t[t] > 0)
+                    for (int c = 0; c < Cfg::kChunks; ++c)
+                        tma_load_4d(sQ + t * Cfg::kTileBytes + c * (kTileQ * 128), &maps.q, &sh.q_full, c * 64,
+                                    q0 + t * kTileQ, h, b);
+            int slot_use = 0;
+            bool ok = true;
+            for (int j = 0; j < n_max && ok; ++j) {
+                if (key_tile_state(p, b, h, j) == 0) continue;
+                for (int which = 0; which < 2 && ok; ++which) {  // K tile, then V tile
+                    const int slot = slot_use % Cfg::kStages, round = slot_use / Cfg::kStages;
+                    if (round > 0) ok = mbar_wait(&sh.kv_empty[slot], (round - 1) & 1, abort_word, 10);
+                    if (!ok) break;
+                    mbar_expect_tx(&sh.kv_full[slot], Cfg::kTileBytes);
+                    const CUtensorMap* map = which == 0 ? &maps.k : &maps.v;
+                    for (int c = 0; c < Cfg::kChunks; ++c)
+                        tma_load_4d(sKV + slot * Cfg::kTileBytes + c * (kTileK * 128), map, &sh.kv_full[slot], c * 64,
+                                    j * kTileK, kvh, b);
+                    ++slot_use;
+                }
+            }
+        }
+      } else if (warp == 8) {
+        // ------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = umma_idesc(kTileQ, kTileK, BF16 ? 1 : 0, false, false);
+            constexpr uint32_t idesc_o = umma_idesc(kTileQ, D, BF16 ? 1 : 0, false, true);
+            const uint32_t q_addr = smem_u32(sQ), kv_addr = smem_u32(sKV);
+            auto issue_s = [&](int t, int slot) {
+                const uint32_t a0 = q_addr + t * Cfg::kTileBytes, b0 = kv_addr + slot * Cfg::kTileBytes;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * (kTileQ * 128) + (kk % 4) * 32;
+                    umma_ss(tmem + t * 128, umma_desc_sw128(a0 + off, 16, 1024), umma_desc_sw128(b0 + off, 16, 1024),
+                            idesc_s, kk > 0);
+                }
+            };
+            auto issue_o = [&](int t, int slot, bool accumulate) {
+                const uint32_t b0 = kv_addr + slot * Cfg::kTileBytes;
+#pragma unroll
+                for (int kk = 0; kk < kTileK / 16; ++kk)
+                    umma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8,
+                            umma_desc_sw128(b0 + kk * 2048, kTileK * 128, 1024), idesc_o, accumulate || kk > 0);
+            };
+            bool ok = mbar_wait(&sh.q_full, 0, abort_word, 20);
+            int slot_use = 0, iter[2] = {0, 0};
+            // first visible key tile
+            int j = 0;
+            while (j < n_max && key_tile_state(p, b, h, j) == 0) ++j;
+            if (ok && j < n_max) {
+                const int slot = slot_use % Cfg::kStages;
+                ok = mbar_wait(&sh.kv_full[slot], (slot_use / Cfg::kStages) & 1, abort_word, 21);
+                if (ok) {
+                    tc_fence_after();
+                    for (int t = 0; t < 2; ++t)
+                        if (j < n_t[t]) {
+                            issue_s(t, slot);
+                            umma_commit(&sh.s_ready[t]);
+                        }
+                    umma_commit(&sh.kv_empty[slot]);
+                    ++slot_use;
+                }
+            }
+            while (ok && j < n_max) {
+                int jn = j + 1;
+                while (jn < n_max && key_tile_state(p, b, h, jn) == 0) ++jn;
+                const int v_slot = slot_use % Cfg::kStages, v_par = (slot_use / Cfg::kStages) & 1;
+                ++slot_use;
+                int k_slot = -1, k_par = 0;
+                if (jn < n_max) {
+                    k_slot = slot_use % Cfg::kStages;
+                    k_par = (slot_use / Cfg::kStages) & 1;
+                    ++slot_use;
+                }
+                ok = mbar_wait(&sh.kv_full[v_slot], v_par, abort_word, 22);
+                bool k_waited = false;
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (j >= n_t[t]) continue;
+                    ok = mbar_wait(&sh.p_ready[t], iter[t] & 1, abort_word, 23 + t);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_o(t, v_slot, iter[t] > 0);
+                    if (jn < n_t[t]) {
+                        if (!k_waited) {
+                            ok = mbar_wait(&sh.kv_full[k_slot], k_par, abort_word, 25);
+                            if (!ok) break;
+                            tc_fence_after();
+                            k_waited = true;
+                        }
+                        issue_s(t, k_slot);
+                    }
+                    umma_commit(&sh.s_ready[t]);
+                    ++iter[t];
+                }
+                if (!ok) break;
+                umma_commit(&sh.kv_empty[v_slot]);
+                if (k_slot >= 0) umma_commit(&sh.kv_empty[k_slot]);
+                j = jn;
+            }
+        }
+      }
+    } else {
+        reg_alloc<232>();
+        // ---------------------------------------------------------- softmax
+        const int t = warp >> 2;
+        const int row_in_tile = (warp & 3) * 32 + lane;
+        const int row = q0 + t * kTileQ + row_in_tile;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+        const uint32_t s_addr = lane_base + t * 128, o_addr = lane_base + 256 + t * 128;
+        const float sign = p.scale >= 0.f ? 1.f : -1.f;
+        const float c2 = fabsf(p.scale) * kLog2e;
+        const uint8_t* kmask = p.has_mask ? p.mask + (int64_t)b * p.ms[0] + (int64_t)h * p.ms[1] : nullptr;
+        float m_used = -INFINITY, m_true = -INFINITY, l = 0.f;
+        int iter = 0;
+        bool ok = true;
+        for (int j = 0; j < n_t[t] && ok; ++j) {
+            const int state = key_tile_state(p, b, h, j);
+            if (state == 0) continue;
+            ok = mbar_wait(&sh.s_ready[t], iter & 1, abort_word, 30 + t);
+            if (!ok) break;
+            tc_fence_after();
+            float s[kTileK];
+#pragma unroll
+            for (int c = 0; c < kTileK; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(s_addr + c, r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(r[i]);
+            }
+            tmem_wait_ld();
+            if (sign < 0.f) {
+#pragma unroll
+                for (int c = 0; c < kTileK; ++c) s[c] = -s[c];
+            }
+            const int key0 = j * kTileK;
+            const bool partial = (key0 + kTileK > p.Sk) || (p.causal && key0 + kTileK - 1 > q0 + t * kTileQ) ||
+                                 state == 1;
+            if (partial) {
+#pragma unroll
+                for (int c = 0; c < kTileK; ++c) {
+                    const int key = key0 + c;
+                    bool vis = key < p.Sk && (!p.causal || key <= row);
+                    if (vis && kmask) vis = kmask[(int64_t)key * p.ms[3]] != 0;
+                    s[c] = vis ? s[c] : -INFINITY;
+                }
+            }
+            float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+#pragma unroll
+            for (int c = 4; c < kTileK; c += 4) {
+                mx0 = fmaxf(mx0, s[c]);
+                mx1 = fmaxf(mx1, s[c + 1]);
+                mx2 = fmaxf(mx2, s[c + 2]);
+                mx3 = fmaxf(mx3, s[c + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            m_true = fmaxf(m_true, mx);
+            const bool rebase = mx > m_used && (m_used == -INFINITY || (mx - m_used) * c2 > kRebase);
+            float alpha = 1.f;
+            if (rebase) {
+                alpha = (m_used == -INFINITY) ? 0.f : ex2((m_used - mx) * c2);
+                l *= alpha;
+                m_used = mx;
+            }
+            if (iter > 0 && __any_sync(0xffffffffu, rebase)) {
+#pragma unroll
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(o_addr + c, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    tmem_st32(o_addr + c, r);
+                }
+            }
+            const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < kTileK; c += 32) {
+                uint32_t w[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float pa = ex2((s[c + 2 * i] - m_safe) * c2);
+                    float pb = ex2((s[c + 2 * i + 1] - m_safe) * c2);
+                    if (partial) {  // hidden entries carry -inf; keep them at zero also when |scale| is 0
+                        pa = s[c + 2 * i] == -INFINITY ? 0.f : pa;
+                        pb = s[c + 2 * i + 1] == -INFINITY ? 0.f : pb;
+                    }
+                    sum0 += pa;
+                    sum1 += pb;
+                    w[i] = pack2<BF16>(pa, pb);
+                }
+                tmem_st16(s_addr + c / 2, w);
+            }
+            l += sum0 + sum1;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sh.p_ready[t]);
+            ++iter;
+        }
+        // epilogue: wait for the last product, normalise, store
+        if (ok && iter == 0 && row < p.Sq && n_t[t] > 0) {
+            // every key tile of this row is hidden: zero output, empty statistics
+            using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+            T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] + (int64_t)row * p.os[2];
+            const int64_t si = ((int64_t)b * p.Hq + h) * p.Sq + row;
+            for (int d = 0; d < D; d += 8) *reinterpret_cast<uint4*>(orow + d) = make_uint4(0, 0, 0, 0);
+            p.maximum[si] = -INFINITY;
+            p.logsum[si] = 0.f;
+        }
+        if (iter > 0) {
+            if (ok) ok = mbar_wait(&sh.s_ready[t], iter & 1, abort_word, 32 + t);
+            if (ok) {
+                tc_fence_after();
+                using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+                T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] +
+                          (int64_t)row * p.os[2];
+                const float den = l > 0.f ? l : 1.f;
+#pragma unroll
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(o_addr + c, r);
+                    tmem_wait_ld();
+                    if (row < p.Sq) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 w;
+                            w.x = pack2<BF16>(__uint_as_float(r[i]) / den, __uint_as_float(r[i + 1]) / den);
+                            w.y = pack2<BF16>(__uint_as_float(r[i + 2]) / den, __uint_as_float(r[i + 3]) / den);
+                            w.z = pack2<BF16>(__uint_as_float(r[i + 4]) / den, __uint_as_float(r[i + 5]) / den);
+                            w.w = pack2<BF16>(__uint_as_float(r[i + 6]) / den, __uint_as_float(r[i + 7]) / den);
+                            *reinterpret_cast<uint4*>(orow + c + i) = w;
+                        }
+                    }
+                }
+                if (row < p.Sq) {
+                    const int64_t si = ((int64_t)b * p.Hq + h) * p.Sq + row;
+                    p.maximum[si] = m_true;
+                    p.logsum[si] = l > 0.f ? log2f(l) + (m_used - m_true) * c2 : 0.f;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 1000 + sh.abort_word;
+    if (warp == 8) tmem_dealloc(tmem, 512);
+}
+
+std::atomic<int> g_configured{0};
+
+template <int D, bool BF16>
+cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
+    using Cfg = FwdCfg<D>;
+    // The shared-memory opt-in is per device; it is cheap, so it is simply repeated per call.
+    cudaError_t e = cudaFuncSetAttribute(pipeline_forward<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    constexpr int variant = (D == 128 ? 0 : 2) + (BF16 ? 0 : 1);
+    const int bit = 1 << variant;
+    if (!(g_configured.load() & bit)) g_configured |= bit;
+    FwdMaps maps;
+    const CUtensorMapDataType dt = BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (!encode_bhsd_map(&maps.q, p.q, dt, p.D, p.Sq, p.Hq, p.B, p.qs, 64, kTileQ)) return cudaErrorInvalidValue;
+    if (!encode_bhsd_map(&maps.k, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kTileK)) return cudaErrorInvalidValue;
+    if (!encode_bhsd_map(&maps.v, p.v, dt, p.D, p.Sk, p.Hkv, p.B, p.vs, 64, kTileK)) return cudaErrorInvalidValue;
+    const int64_t grid = (int64_t)((p.Sq + 2 * kTileQ - 1) / (2 * kTileQ)) * p.B * p.Hq;
+    pipeline_forward<D, BF16><<<(unsigned)grid, kThreads, Cfg::kSmemBytes, st>>>(maps, p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool pipeline_forward_supported(const AttnParams& p, bool bf16) {
+    (void)bf16;
+    if (p.D != 64 && p.D != 128) return false;
+    if (p.nd != 0) return false;
+    if (p.has_mask && p.ms[2] != 0) return false;  // only masks broadcast over the query axis
+    if (!tma_compatible(p.q, p.qs, p.B, p.Hq, p.Sq) || !tma_compatible(p.k, p.ks, p.B, p.Hkv, p.Sk) ||
+        !tma_compatible(p.v, p.vs, p.B, p.Hkv, p.Sk))
+        return false;
+    if (!tma_compatible(p.out, p.os, p.B, p.Hq, p.Sq)) return false;  // 16-byte vector stores per row
+    return true;
+}
+
+cudaError_t launch_pipeline_forward(const AttnParams& p, bool bf16, cudaStream_t st) {
+    if (p.D == 128) return bf16 ? launch_t<128, true>(p, st) : launch_t<128, false>(p, st);
+    return bf16 ? launch_t<64, true>(p, st) : launch_t<64, false>(p, st);
+}
+
+int pipeline_forward_variants() { return __builtin_popcount(g_configured.load()); }
+void pipeline_forward_forget() { g_configured = 0; }
+
+}  // namespace kfa

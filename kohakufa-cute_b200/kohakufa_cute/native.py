@@ -1,0 +1,252 @@
+"""ctypes binding of the C-ABI CUDA library (``libkfa.so``, declared in ``include/kfa.h``).
+
+This module plays the role of the reference's compiled host launcher
+(``src/kohakufa_cute/native.cpp`` of the reference project): it allocates outputs
+and scratch with the PyTorch caching allocator, describes every tensor to the
+library as a plain pointer/size/stride record and launches on the current
+stream.  There is no fallback: when the library is missing, loading raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIBRARY_PATH = os.path.join(_HERE, "libkfa.so")
+
+KFA_F16, KFA_BF16, KFA_F32, KFA_BOOL, KFA_I32 = range(5)
+_DTYPES = {
+    torch.float16: KFA_F16,
+    torch.bfloat16: KFA_BF16,
+    torch.float32: KFA_F32,
+    torch.bool: KFA_BOOL,
+    torch.int32: KFA_I32,
+}
+
+
+class KfaTensor(ctypes.Structure):
+    _fields_ = [
+        ("data", ctypes.c_void_p),
+        ("dtype", ctypes.c_int32),
+        ("ndim", ctypes.c_int32),
+        ("sizes", ctypes.c_int64 * 6),
+        ("strides", ctypes.c_int64 * 6),
+    ]
+
+
+_TP = ctypes.POINTER(KfaTensor)
+_I64P = ctypes.POINTER(ctypes.c_int64)
+
+# name -> (restype, argtypes); must list every symbol declared in include/kfa.h
+SIGNATURES = {
+    "kfa_version": (ctypes.c_int, []),
+    "kfa_last_error": (ctypes.c_char_p, []),
+    "kfa_forward": (ctypes.c_int, [_TP, _TP, _TP, _TP, _TP, _TP, _TP, _TP, ctypes.c_float, ctypes.c_int,
+                                   ctypes.c_void_p]),
+    "kfa_backward_workspace_bytes": (ctypes.c_size_t, [_TP, _TP]),
+    "kfa_backward": (ctypes.c_int, [_TP] * 12 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float, ctypes.c_int,
+                                                 ctypes.c_void_p]),
+    "kfa_center_keys_workspace_bytes": (ctypes.c_size_t, [_TP]),
+    "kfa_center_keys": (ctypes.c_int, [_TP, _TP, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "kfa_neighborhood_forward": (ctypes.c_int, [_TP] * 6 + [_I64P, ctypes.c_int, _I64P, ctypes.c_float,
+                                                            ctypes.c_void_p]),
+    "kfa_neighborhood_backward_workspace_bytes": (ctypes.c_size_t, [_TP]),
+    "kfa_neighborhood_backward": (ctypes.c_int, [_TP] * 10 + [ctypes.c_void_p, ctypes.c_size_t, _I64P, ctypes.c_int,
+                                                              _I64P, ctypes.c_float, ctypes.c_void_p]),
+    "kfa_merge_partial": (ctypes.c_int, [_TP] * 6 + [ctypes.c_float, ctypes.c_void_p]),
+    "kfa_cache_size": (ctypes.c_int, []),
+    "kfa_clear_cache": (None, []),
+    "kfa_launch_count": (ctypes.c_uint64, []),
+    "kfa_device_status": (ctypes.c_int, [ctypes.c_int]),
+    "kfa_selected_family": (ctypes.c_int, [_TP, _TP, _TP, _TP, ctypes.c_int, ctypes.c_int]),
+}
+
+_lock = threading.Lock()
+_library = None
+
+
+def library():
+    """Loads ``libkfa.so`` once; raises ``RuntimeError`` if it has not been built."""
+    global _library
+    if _library is None:
+        with _lock:
+            if _library is None:
+                if not os.path.exists(LIBRARY_PATH):
+                    raise RuntimeError(
+                        f"{LIBRARY_PATH} is missing: build it with `python kohakufa-cute_b200/build.py` "
+                        "(there is no non-CUDA fallback)."
+                    )
+                lib = ctypes.CDLL(LIBRARY_PATH)
+                for name, (restype, argtypes) in SIGNATURES.items():
+                    fn = getattr(lib, name)
+                    fn.restype = restype
+                    fn.argtypes = argtypes
+                _library = lib
+    return _library
+
+
+def loaded():
+    return _library is not None
+
+
+def describe(tensor):
+    """Non-owning ``kfa_tensor`` record for a torch tensor (None -> NULL pointer)."""
+    if tensor is None:
+        return None
+    record = KfaTensor()
+    record.data = tensor.data_ptr()
+    record.dtype = _DTYPES[tensor.dtype]
+    record.ndim = tensor.dim()
+    for axis, (size, stride) in enumerate(zip(tensor.shape, tensor.stride())):
+        record.sizes[axis] = size
+        record.strides[axis] = stride
+    return record
+
+
+def _ref(record):
+    return None if record is None else ctypes.byref(record)
+
+
+def _check(code):
+    if code == 0:
+        return
+    message = library().kfa_last_error().decode()
+    if code == 1:
+        raise ValueError(message)
+    raise RuntimeError(f"libkfa error {code}: {message}")
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _plain(tensor):
+    """Physical storage must equal logical values: resolve lazy conj/neg view flags."""
+    return tensor.resolve_conj().resolve_neg()
+
+
+def _blocks_shape(q, k, mask):
+    return (
+        1 if mask.stride(0) == 0 else q.shape[0],
+        1 if mask.stride(1) == 0 else q.shape[1],
+        1 if mask.stride(2) == 0 else (q.shape[2] + 63) // 64,
+        1 if mask.stride(3) == 0 else (k.shape[2] + 63) // 64,
+    )
+
+
+def forward(q, k, v, mask, scale, causal):
+    """(out, maximum, logsum, blocks) - mirrors the reference extension's ``forward`` (native.cpp:1034)."""
+    lib = library()
+    q, k, v = _plain(q), _plain(k), _plain(v)
+    with torch.cuda.device(q.device):
+        out = torch.empty_like(q)
+        maximum = torch.empty(q.shape[:-1], device=q.device, dtype=torch.float32)
+        logsum = torch.empty_like(maximum)
+        if mask is None:
+            blocks = torch.empty((1, 1, 1, 1), device=q.device, dtype=torch.int32)
+        else:
+            blocks = torch.empty(_blocks_shape(q, k, mask), device=q.device, dtype=torch.int32)
+        records = [describe(t) for t in (q, k, v, mask, out, maximum, logsum, blocks if mask is not None else None)]
+        _check(lib.kfa_forward(*[_ref(r) for r in records], float(scale), int(bool(causal)), _stream(q.device)))
+    return out, maximum, logsum, blocks
+
+
+def backward(q, k, v, mask, maximum, logsum, dout, blocks, out, scale, causal):
+    """(dq, dk, dv) - mirrors the reference extension's ``backward`` (native.cpp:1038)."""
+    lib = library()
+    q, k, v, dout, out = _plain(q), _plain(k), _plain(v), _plain(dout), _plain(out)
+    with torch.cuda.device(q.device):
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        rq, rk = describe(q), describe(k)
+        need = lib.kfa_backward_workspace_bytes(_ref(rq), _ref(rk))
+        workspace = torch.empty(need, device=q.device, dtype=torch.uint8)
+        records = [rq, rk, describe(v), describe(mask), describe(out), describe(maximum), describe(logsum),
+                   describe(dout), describe(blocks if mask is not None else None), describe(dq), describe(dk),
+                   describe(dv)]
+        _check(lib.kfa_backward(*[_ref(r) for r in records], ctypes.c_void_p(workspace.data_ptr()), need,
+                                float(scale), int(bool(causal)), _stream(q.device)))
+    return dq, dk, dv
+
+
+def center_keys(k):
+    """round(f32(k) - mean_S f32(k)) in k's dtype (also the gradient projection of that map)."""
+    lib = library()
+    k = _plain(k)
+    with torch.cuda.device(k.device):
+        out = torch.empty_like(k)
+        rk = describe(k)
+        need = lib.kfa_center_keys_workspace_bytes(_ref(rk))
+        workspace = torch.empty(need, device=k.device, dtype=torch.uint8)
+        ro = describe(out)
+        _check(lib.kfa_center_keys(_ref(rk), _ref(ro), ctypes.c_void_p(workspace.data_ptr()), need,
+                                   _stream(k.device)))
+    return out
+
+
+def _int64_array(values):
+    return (ctypes.c_int64 * len(values))(*[int(x) for x in values])
+
+
+def neighborhood_forward(q, k, v, spatial, window, scale):
+    """(out, maximum, logsum) - mirrors ``neighborhood_forward`` (native.cpp:1043)."""
+    lib = library()
+    q, k, v = _plain(q), _plain(k), _plain(v)
+    with torch.cuda.device(q.device):
+        out = torch.empty_like(q)
+        maximum = torch.empty(q.shape[:-1], device=q.device, dtype=torch.float32)
+        logsum = torch.empty_like(maximum)
+        records = [describe(t) for t in (q, k, v, out, maximum, logsum)]
+        _check(lib.kfa_neighborhood_forward(*[_ref(r) for r in records], _int64_array(spatial), len(spatial),
+                                            _int64_array(window), float(scale), _stream(q.device)))
+    return out, maximum, logsum
+
+
+def neighborhood_backward(q, k, v, out, maximum, logsum, dout, spatial, window, scale):
+    lib = library()
+    q, k, v, out, dout = (_plain(t) for t in (q, k, v, out, dout))
+    with torch.cuda.device(q.device):
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        rq = describe(q)
+        need = lib.kfa_neighborhood_backward_workspace_bytes(_ref(rq))
+        workspace = torch.empty(need, device=q.device, dtype=torch.uint8)
+        records = [rq] + [describe(t) for t in (k, v, out, maximum, logsum, dout, dq, dk, dv)]
+        _check(lib.kfa_neighborhood_backward(*[_ref(r) for r in records], ctypes.c_void_p(workspace.data_ptr()), need,
+                                             _int64_array(spatial), len(spatial), _int64_array(window), float(scale),
+                                             _stream(q.device)))
+    return dq, dk, dv
+
+
+def merge_partial(acc_out, acc_maximum, acc_logsum, part_out, part_maximum, part_logsum, scale):
+    """In-place (max, sum) merge of one partial attention result into the running FP32 result."""
+    lib = library()
+    with torch.cuda.device(acc_out.device):
+        records = [describe(t) for t in (acc_out, acc_maximum, acc_logsum, part_out, part_maximum, part_logsum)]
+        _check(lib.kfa_merge_partial(*[_ref(r) for r in records], float(scale), _stream(acc_out.device)))
+
+
+def selected_family(q, k, v, mask=None, causal=False, backward=False):
+    """0 = general kernels, 1 = tcgen05 tensor-memory pipeline."""
+    lib = library()
+    with torch.cuda.device(q.device):
+        records = [describe(t) for t in (q, k, v, mask)]
+        return lib.kfa_selected_family(*[_ref(r) for r in records], int(bool(causal)), int(bool(backward)))
+
+
+def cache_size():
+    return library().kfa_cache_size()
+
+
+def clear_cache():
+    library().kfa_clear_cache()
+
+
+def launch_count():
+    return int(library().kfa_launch_count())
+
+
+def device_status(reset=False):
+    return library().kfa_device_status(int(reset))

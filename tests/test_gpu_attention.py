@@ -1,0 +1,412 @@
+"""GPU parity tests: the CUDA path (through the public API and the C ABI) against the CPU oracle."""
+
+import math
+
+import pytest
+import torch
+
+from oracle import attention_oracle as ao
+from tests.golden_io import ATTENTION_CASES, attention_case, load
+from tests.helpers import (NAMES, TOL, check_against_oracle, make_inputs, run_attention, strided_like_projection)
+
+pytestmark = pytest.mark.gpu
+
+
+def api():
+    import kohakufa_cute
+
+    return kohakufa_cute
+
+
+def native():
+    from kohakufa_cute import native as n
+
+    return n
+
+
+@pytest.fixture(autouse=True)
+def _device_status_clean():
+    yield
+    torch.cuda.synchronize()
+    assert native().device_status(reset=True) == 0, "a kernel reported a bounded-wait timeout"
+
+
+# ------------------------------------------------------------------ golden vectors
+@pytest.mark.parametrize("index", ATTENTION_CASES)
+def test_golden_cases(index):
+    c = attention_case(index)
+    q, k, v, dout = (c[n].cuda() for n in ("q", "k", "v", "dout"))
+    mask = None if c["mask"] is None else c["mask"].cuda()
+    actual = run_attention(api().attention, q, k, v, dout, mask=mask, causal=c["causal"], scale=c["scale"])
+    check_against_oracle(actual, q, k, v, dout, mask, c["causal"], c["scale"], label=f"case{index} ")
+    # the committed reference answers themselves (FP64 mathematics from the reference project)
+    tol = TOL[q.dtype]["norm"]
+    for name, got in zip(NAMES, actual):
+        want = c[f"exact_{name}"]
+        if float(want.abs().max()) > 0:
+            assert ao.per_head_relative_error(got.cpu(), want) < tol, name
+
+
+# ---------------------------------------------------------------- shape sweeps
+PIPELINE_SHAPES = [
+    # B, Hq, Hkv, Sq, Sk, D, causal
+    (1, 1, 1, 128, 128, 128, False),
+    (1, 2, 1, 256, 256, 128, True),
+    (2, 4, 2, 129, 257, 128, False),
+    (1, 2, 2, 300, 300, 128, True),
+    (1, 2, 1, 1, 300, 128, False),
+    (1, 4, 1, 17, 127, 64, True),
+    (1, 2, 2, 513, 140, 64, True),
+    (1, 2, 2, 140, 513, 64, True),
+    (1, 8, 2, 640, 640, 64, False),
+    (1, 2, 1, 1024, 1024, 128, True),
+]
+
+
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
+@pytest.mark.parametrize("shape", PIPELINE_SHAPES)
+def test_pipeline_shapes(shape, dtype):
+    B, Hq, Hkv, Sq, Sk, D, causal = shape
+    q, k, v, dout = make_inputs(B, Hq, Hkv, Sq, Sk, D, dtype, seed=hash(shape) % 1000)
+    assert native().selected_family(q, k, v, None, causal) == 1
+    actual = run_attention(api().attention, q, k, v, dout, causal=causal)
+    check_against_oracle(actual, q, k, v, dout, None, causal, None)
+
+
+GENERAL_SHAPES = [
+    (1, 2, 1, 33, 49, 1, False),
+    (1, 2, 2, 70, 65, 17, True),
+    (1, 4, 2, 64, 96, 80, False),
+    (1, 2, 1, 130, 130, 96, True),
+    (1, 2, 2, 65, 200, 256, False),
+    (1, 2, 1, 96, 96, 512, True),
+    (1, 1, 1, 40, 40, 257, False),
+]
+
+
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
+@pytest.mark.parametrize("shape", GENERAL_SHAPES)
+def test_general_head_dims(shape, dtype):
+    B, Hq, Hkv, Sq, Sk, D, causal = shape
+    q, k, v, dout = make_inputs(B, Hq, Hkv, Sq, Sk, D, dtype, seed=D)
+    actual = run_attention(api().attention, q, k, v, dout, causal=causal)
+    check_against_oracle(actual, q, k, v, dout, None, causal, None)
+
+
+@pytest.mark.parametrize("scale", (0.0, -0.125, 0.3))
+@pytest.mark.parametrize("D", (64, 96))
+def test_signed_and_zero_scale(scale, D):
+    q, k, v, dout = make_inputs(1, 2, 1, 150, 170, D, torch.bfloat16, seed=11)
+    actual = run_attention(api().attention, q, k, v, dout, scale=scale, causal=True)
+    check_against_oracle(actual, q, k, v, dout, None, True, scale)
+    if scale == 0.0:
+        assert float(actual[1].abs().max()) == 0 and float(actual[2].abs().max()) == 0
+
+
+# ------------------------------------------------------------------------ masks
+def _mask_variants(B, Hq, Sq, Sk, gen):
+    full = torch.rand(Sq, Sk, generator=gen) > 0.3
+    full[0] = False
+    return {
+        "keys": torch.rand(Sk, generator=gen) > 0.3,
+        "key_padding": (torch.arange(Sk)[None, None, None, :] < torch.tensor([Sk - 37, Sk // 2])[:B, None, None, None]),
+        "full2d": full,
+        "full4d_one": full[None, None],
+        "per_head": torch.rand(B, Hq, Sq, Sk, generator=gen) > 0.5,
+        "all_true": torch.ones(1, 1, 1, 1, dtype=torch.bool),
+        "all_false": torch.zeros(1, 1, 1, 1, dtype=torch.bool),
+    }
+
+
+@pytest.mark.parametrize("D", (64, 128, 80))
+@pytest.mark.parametrize("causal", (False, True))
+@pytest.mark.parametrize("name", ("keys", "key_padding", "full2d", "full4d_one", "per_head", "all_true", "all_false"))
+def test_boolean_masks(name, causal, D):
+    B, Hq, Hkv, Sq, Sk = 2, 4, 2, 150, 330
+    gen = torch.Generator().manual_seed(31)
+    mask = _mask_variants(B, Hq, Sq, Sk, gen)[name].cuda()
+    q, k, v, dout = make_inputs(B, Hq, Hkv, Sq, Sk, D, torch.bfloat16, seed=32)
+    actual = run_attention(api().attention, q, k, v, dout, mask=mask, causal=causal)
+    _, contract = check_against_oracle(actual, q, k, v, dout, mask, causal, None)
+    # all-hidden rows give exactly zero output and zero dQ
+    seen = ao.visible_pairs(B, Hq, Sq, Sk, mask.cpu(), causal)
+    hidden = ~seen.any(-1)
+    if bool(hidden.any()):
+        assert float(actual[0].cpu()[hidden].abs().max()) == 0
+        assert float(actual[1].cpu()[hidden].abs().max()) == 0
+
+
+def test_key_padding_long_sequence_skips_hidden_tiles():
+    B, H, S, D = 2, 2, 2048, 128
+    q, k, v, dout = make_inputs(B, H, H, S, S, D, torch.bfloat16, seed=5)
+    mask = (torch.arange(S) < int(S * 0.9))[None, None, None, :].expand(B, 1, 1, S).cuda()
+    assert native().selected_family(q, k, v, mask.expand(B, H, S, S), False) == 1
+    actual = run_attention(api().attention, q, k, v, dout, mask=mask)
+    check_against_oracle(actual, q, k, v, dout, mask, False, None)
+    assert float(actual[2][:, :, int(S * 0.9):].abs().max()) == 0
+    assert float(actual[3][:, :, int(S * 0.9):].abs().max()) == 0
+
+
+# ---------------------------------------------------------- layouts and strides
+@pytest.mark.parametrize("D", (64, 128, 96))
+def test_projection_layout_preserves_strides(D):
+    q, k, v, dout = make_inputs(2, 4, 2, 200, 260, D, torch.bfloat16, seed=41)
+    qs, ks, vs = (strided_like_projection(t) for t in (q, k, v))
+    leaves = [t.detach().requires_grad_(True) for t in (qs, ks, vs)]
+    out = api().attention(*leaves, causal=True)
+    assert out.stride() == qs.stride()
+    grads = torch.autograd.grad(out, leaves, dout)
+    for g, t in zip(grads, (qs, ks, vs)):
+        assert g.stride() == t.stride()
+    check_against_oracle((out.detach(), *grads), q, k, v, dout, None, True, None)
+
+
+def test_cache_slices_ignore_poison_beyond_the_view():
+    B, H, S, D, cap = 1, 2, 150, 128, 256
+    q, k, v, dout = make_inputs(B, H, H, S, S, D, torch.bfloat16, seed=43)
+    big_k = torch.full((B, H, cap, D), float("nan"), device="cuda", dtype=torch.bfloat16)
+    big_v = torch.full((B, H, cap, D), 1234.0, device="cuda", dtype=torch.bfloat16)
+    big_k[:, :, :S], big_v[:, :, :S] = k, v
+    actual = run_attention(api().attention, q, big_k[:, :, :S], big_v[:, :, :S], dout)
+    check_against_oracle(actual, q, k, v, dout)
+
+
+def test_expanded_and_offset_output_gradients():
+    q, k, v, _ = make_inputs(1, 2, 2, 140, 140, 128, torch.bfloat16, seed=44)
+    leaves = [t.detach().requires_grad_(True) for t in (q, k, v)]
+    out = api().attention(*leaves, causal=True)
+    out.sum().backward()  # dO is an expanded (all strides zero) tensor of ones
+    actual = (out.detach(), leaves[0].grad, leaves[1].grad, leaves[2].grad)
+    check_against_oracle(actual, q, k, v, torch.ones_like(q), None, True, None)
+
+
+def test_singleton_key_is_exact():
+    q, k, v, dout = make_inputs(2, 4, 2, 70, 1, 64, torch.bfloat16, seed=45)
+    out, dq, dk, dv = run_attention(api().attention, q, k, v, dout)
+    assert torch.equal(out, v.repeat_interleave(2, 1).expand_as(out))
+    assert float(dq.abs().max()) == 0 and float(dk.abs().max()) == 0
+    want = dout.float().reshape(2, 2, 2, 70, 64).sum((2, 3))[:, :, None]
+    torch.testing.assert_close(dv.float(), want, atol=0.02, rtol=0.02)
+
+
+# ------------------------------------------------------------------- statistics
+@pytest.mark.parametrize("D,Sq,Sk,causal", ((128, 300, 300, True), (64, 1, 300, False), (80, 33, 49, False)))
+def test_saved_statistics(D, Sq, Sk, causal):
+    q, k, v, _ = make_inputs(1, 4, 2, Sq, Sk, D, torch.bfloat16, seed=51, q_scale=4.0)
+    scale = -0.2
+    out, maximum, logsum, _ = native().forward(q, k, v, None, scale, causal)
+    want_max, want_log = ao.forward_statistics((q.cpu(), k.cpu(), v.cpu()), None, causal, scale)
+    torch.testing.assert_close(maximum.cpu().double(), want_max, atol=1e-3, rtol=1e-5)
+    torch.testing.assert_close(logsum.cpu().double(), want_log, atol=2e-3, rtol=1e-4)
+    keys = k.cpu().double().repeat_interleave(2, 1)
+    logits = (q.cpu().double() @ keys.transpose(-1, -2)) * scale
+    if causal:
+        logits = logits.masked_fill(~ao.visible_pairs(1, 4, Sq, Sk, None, True), -math.inf)
+    combined = maximum.cpu().double() * abs(scale) + logsum.cpu().double() * math.log(2)
+    torch.testing.assert_close(combined, torch.logsumexp(logits, -1), atol=2e-3, rtol=1e-4)
+
+
+# ------------------------------------------------------------ directed fixtures
+def test_saturated_pair_keeps_a_nonzero_query_gradient():
+    c = load("saturated_pair")
+    q, k, v, dout = (c[n].cuda() for n in ("q", "k", "v", "dout"))
+    out, dq, dk, dv = run_attention(api().attention, q, k, v, dout, scale=1.0)
+    assert abs(float(dv[0, 0, 0, 0]) - 1.0) < 0.02
+    want = float(c["rounded_dk"][0, 0, 1, 0])
+    assert want != 0 and abs(float(dk[0, 0, 1, 0]) / want - 1) < 0.03
+
+
+@pytest.mark.parametrize("dimension", (16, 128))
+def test_key_cancellation_fixture(dimension):
+    c = load(f"key_cancellation_d{dimension}")
+    q, k, v, dout = (c[n].cuda() for n in ("q", "k", "v", "dout"))
+    actual = run_attention(api().attention, q, k, v, dout)
+    check_against_oracle(actual, q, k, v, dout)
+
+
+def test_large_logits_stay_finite_and_accurate():
+    # clustered unit directions scaled so that scaled logits reach ~1e5: needs the shifted score
+    gen = torch.Generator().manual_seed(61)
+    H, S, D = 2, 384, 128
+    centers = torch.randn(1, H, 16, D, generator=gen)
+    centers = centers / centers.norm(dim=-1, keepdim=True)
+    pick = torch.randint(16, (1, H, S), generator=gen)
+    base = centers.gather(2, pick[..., None].expand(-1, -1, -1, D))
+    radius = math.sqrt(1e5 * math.sqrt(D))
+    q, k = ((radius * (base + 0.03 * torch.randn(base.shape, generator=gen))).to(torch.bfloat16).cuda() for _ in range(2))
+    v, dout = (torch.randn(base.shape, generator=gen).to(torch.bfloat16).cuda() for _ in range(2))
+    actual = run_attention(api().attention, q, k, v, dout, causal=True)
+    exact = ao.math_reference((q.cpu(), k.cpu(), v.cpu()), dout.cpu(), None, True, None)
+    for name, got, want in zip(NAMES, actual, exact):
+        assert bool(torch.isfinite(got).all()), name
+    got, want = actual[3].cpu().double().flatten(), exact[3].flatten()
+    assert float(torch.dot(got, want) / (got.norm() * want.norm())) > 0.9999
+    got, want = actual[0].cpu().double().flatten(), exact[0].flatten()
+    assert float(torch.dot(got, want) / (got.norm() * want.norm())) > 0.9999
+
+
+# ------------------------------------------------------------------ SDPA wrappers
+def test_sdpa_wrappers_and_errors():
+    K = api()
+    q, k, v, dout = make_inputs(1, 4, 2, 130, 130, 64, torch.bfloat16, seed=71)
+    out = K.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+    torch.testing.assert_close(out, K.attention(q, k, v, causal=True), atol=0, rtol=0)
+    torch.testing.assert_close(K.automatic_scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True), out,
+                               atol=0, rtol=0)
+    mask = torch.ones(130, 130, dtype=torch.bool, device="cuda")
+    for kwargs, pattern in (
+        (dict(dropout_p=0.1), "dropout"),
+        (dict(attn_mask=mask, is_causal=True, enable_gqa=True), "folded"),
+        (dict(attn_mask=mask.float(), enable_gqa=True), "boolean"),
+        (dict(), "enable_gqa"),
+    ):
+        with pytest.raises(ValueError, match=pattern):
+            K.scaled_dot_product_attention(q, k, v, **kwargs)
+    with pytest.raises(ValueError, match="FP32"):
+        K.attention(q.float(), k.float(), v.float())
+    with pytest.raises(ValueError, match="CUDA"):
+        K.attention(q.cpu(), k.cpu(), v.cpu())
+    with pytest.raises(ValueError, match="4D"):
+        K.attention(q[0], k[0], v[0])
+    with pytest.raises(ValueError, match="K/V shapes"):
+        K.attention(q, k, v[:, :, :-1])
+    with pytest.raises(ValueError, match="nonempty"):
+        K.attention(q[:, :, :0], k, v)
+    # unsupported inputs of the automatic entry point go to native SDPA unchanged
+    qf, kf, vf = q.float(), k.float()[:, :1].expand(-1, 4, -1, -1), v.float()[:, :1].expand(-1, 4, -1, -1)
+    want = torch.nn.functional.scaled_dot_product_attention(qf, kf, vf)
+    torch.testing.assert_close(K.automatic_scaled_dot_product_attention(qf, kf, vf), want, atol=0, rtol=0)
+
+
+# ------------------------------------------------------------------ key centering
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
+def test_center_keys_kernel_matches_the_contract(dtype):
+    c = load("center_keys_bf16" if dtype == torch.bfloat16 else "center_keys_fp16")
+    got = native().center_keys(c["k"].cuda())
+    # FP32 means may differ in the last bit by summation order: allow one ulp of the 16-bit type
+    diff = (got.cpu().float() - c["centered"].float()).abs()
+    assert float(diff.max()) <= float(c["centered"].float().abs().max()) * 2 ** (-7 if dtype == torch.bfloat16 else -10)
+    keys = (c["k"].transpose(1, 2).contiguous().transpose(1, 2)).cuda()
+    torch.testing.assert_close(native().center_keys(keys), got, atol=0, rtol=0)
+    back = native().center_keys(c["grad"].cuda())
+    assert float(back.float().sum(-2).abs().max()) < 0.05
+
+
+@pytest.mark.parametrize("causal,masked", ((False, False), (True, False), (False, True), (True, True)))
+def test_centered_attention_matches_fp64(causal, masked):
+    gen = torch.Generator().manual_seed(44)
+    q = torch.randn(2, 4, 33, 64, generator=gen).bfloat16().cuda()
+    k = (torch.randn(2, 2, 49, 64, generator=gen) + 4).bfloat16().cuda()
+    v = torch.randn(2, 2, 49, 64, generator=gen).bfloat16().cuda()
+    dout = torch.randn(2, 4, 33, 64, generator=gen).bfloat16().cuda()
+    mask = None
+    if masked:
+        mask = (torch.rand(33, 49, generator=gen) > 0.2)
+        mask[0] = False
+        mask = mask.cuda()
+    actual = run_attention(api().attention, q, k, v, dout, mask=mask, causal=causal, scale=-0.125, center_keys=True)
+    exact = ao.math_reference((q.cpu(), k.cpu(), v.cpu()), dout.cpu(), None if mask is None else mask.cpu(), causal,
+                              -0.125)
+    for name, got, want in zip(NAMES, actual, exact):
+        assert ao.relative_error(got.cpu(), want) < 0.04, name
+    assert float(actual[2].float().sum(-2).abs().max()) < 0.05
+
+
+# ------------------------------------------------- torch.compile and CUDA graphs
+def test_compiled_attention_matches_eager():
+    K = api()
+    q, k, v, dout = make_inputs(1, 4, 2, 200, 200, 128, torch.bfloat16, seed=81)
+    compiled = torch.compile(K.attention, fullgraph=True)
+    eager = run_attention(K.attention, q, k, v, dout, causal=True)
+    traced = run_attention(compiled, q, k, v, dout, causal=True)
+    for a, b in zip(eager, traced):
+        torch.testing.assert_close(a, b, atol=0, rtol=0)
+    eager = run_attention(K.attention, q, k, v, dout, center_keys=True)
+    traced = run_attention(compiled, q, k, v, dout, center_keys=True)
+    for a, b in zip(eager, traced):
+        torch.testing.assert_close(a, b, atol=0, rtol=0)
+
+
+def test_cuda_graph_replay_with_changed_inputs_and_mask():
+    K = api()
+    q, k, v, dout = make_inputs(1, 2, 2, 260, 260, 128, torch.bfloat16, seed=82)
+    mask = (torch.arange(260) < 200)[None, None, None, :].cuda().clone()
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            out = K.attention(*leaves, mask=mask, center_keys=True)
+            torch.autograd.grad(out, leaves, dout)
+    torch.cuda.current_stream().wait_stream(stream)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        out = K.attention(*leaves, mask=mask, center_keys=True)
+        grads = torch.autograd.grad(out, leaves, dout)
+    # new values in the same storage, including a different mask, then replay
+    q2, k2, v2, dout2 = make_inputs(1, 2, 2, 260, 260, 128, torch.bfloat16, seed=83)
+    with torch.no_grad():
+        for leaf, new in zip(leaves, (q2, k2 + 3, v2)):
+            leaf.copy_(new)
+        dout.copy_(dout2)
+        mask.copy_((torch.arange(260) < 131)[None, None, None, :])
+        out.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    want = run_attention(K.attention, leaves[0].detach(), leaves[1].detach(), leaves[2].detach(), dout, mask=mask,
+                         center_keys=True)
+    for got, ref in zip((out, *grads), want):
+        torch.testing.assert_close(got, ref, atol=0, rtol=0)
+
+
+def test_two_streams_give_identical_results():
+    import threading
+
+    K = api()
+    q, k, v, dout = make_inputs(1, 4, 2, 300, 300, 128, torch.bfloat16, seed=84)
+    results = [None, None]
+
+    def work(slot):
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            results[slot] = run_attention(K.attention, q, k, v, dout, causal=True)
+        stream.synchronize()
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for a, b in zip(*results):
+        torch.testing.assert_close(a, b, atol=0, rtol=0)
+    assert native().cache_size() <= 128
+
+
+# --------------------------------------------------------- full-size properties
+def test_llm_gqa_config_row_sampled():
+    """BASELINE config 3 at batch 1: q scaled by 8, keys offset per head, tiny dO; checks sampled rows."""
+    gen = torch.Generator().manual_seed(3)
+    B, Hq, Hkv, S, D = 1, 8, 2, 4096, 128
+    q = (8 * torch.randn(B, Hq, S, D, generator=gen)).bfloat16().cuda()
+    k = (torch.randn(B, Hkv, S, D, generator=gen) + 2 * torch.randn(B, Hkv, 1, D, generator=gen)).bfloat16().cuda()
+    v = torch.randn(B, Hkv, S, D, generator=gen).bfloat16().cuda()
+    dout = (math.sqrt(1e-3) * torch.randn(B, Hq, S, D, generator=gen)).bfloat16().cuda()
+    out, dq, dk, dv = run_attention(api().attention, q, k, v, dout, causal=True)
+    rows = torch.cat([torch.arange(0, 128), torch.arange(S - 128, S), torch.randint(128, S - 128, (128,), generator=gen)])
+    heads = [0, 5]
+    for h in heads:
+        sel = (q[:, h:h + 1].cpu(), k[:, h // 4:h // 4 + 1].cpu(), v[:, h // 4:h // 4 + 1].cpu())
+        part = ao.contract_reference(sel, dout[:, h:h + 1].cpu(), None, True, None, output=out[:, h:h + 1].cpu(),
+                                     query_rows=rows)
+        assert ao.relative_error(out[:, h:h + 1, rows].cpu(), part[0]) < 0.01
+        assert ao.relative_error(dq[:, h:h + 1, rows].cpu(), part[1]) < 0.01
+    # dK/dV of one K/V head need every query row of its four query heads
+    sel = (q[:, :4].cpu(), k[:, :1].cpu(), v[:, :1].cpu())
+    full = ao.contract_reference(sel, dout[:, :4].cpu(), None, True, None, output=out[:, :4].cpu())
+    assert ao.relative_error(dk[:, :1].cpu(), full[2]) < 0.01
+    assert ao.relative_error(dv[:, :1].cpu(), full[3]) < 0.01
+    # centered run: same output within the looser centering gate, sum_S dK == 0
+    outc, dqc, dkc, dvc = run_attention(api().attention, q, k, v, dout, causal=True, center_keys=True)
+    assert ao.relative_error(outc[:, :4].cpu(), full[0]) < 0.04
+    assert ao.relative_error(dvc[:, :1].cpu(), full[3]) < 0.04
+    assert float(dkc.float().sum(-2).abs().max()) < 0.05 * float(dkc.float().abs().max()) * math.sqrt(S)

@@ -1,0 +1,117 @@
+"""GPU parity tests for 2-D / 3-D neighbourhood attention against the CPU oracle."""
+
+import pytest
+import torch
+
+from oracle import attention_oracle as ao
+from oracle import neighborhood_oracle as no
+from tests.golden_io import NEIGHBORHOOD_CASES, load
+from tests.helpers import NAMES, TOL
+
+pytestmark = pytest.mark.gpu
+
+
+def api():
+    import kohakufa_cute
+
+    return kohakufa_cute
+
+
+def run(q, k, v, dout, spatial, window, scale):
+    leaves = [t.detach().clone().requires_grad_(True) for t in (q, k, v)]
+    out = api().neighborhood_attention(*leaves, spatial_shape=spatial, window_size=window, scale=scale)
+    grads = torch.autograd.grad(out, leaves, dout)
+    return (out.detach(), *grads)
+
+
+def gate(actual, q, k, v, dout, spatial, window, scale):
+    tol = TOL[q.dtype]
+    cpu = tuple(t.cpu() for t in (q, k, v))
+    exact = no.na_math_reference(cpu, dout.cpu(), spatial, window, scale)
+    policy = no.na_contract_reference(cpu, dout.cpu(), spatial, window, scale, actual[0].cpu())
+    for name, got, want_exact, want in zip(NAMES, actual, exact, policy):
+        got = got.cpu()
+        assert bool(torch.isfinite(got).all()), name
+        for reference in (want_exact, want):
+            if float(reference.abs().max()) > 0:
+                assert ao.per_head_relative_error(got, reference) < tol["norm"], name
+            else:
+                assert float(got.abs().max()) == 0, name
+        torch.testing.assert_close(got.double(), want, atol=tol["elem"], rtol=tol["elem"])
+
+
+@pytest.mark.parametrize("index", NEIGHBORHOOD_CASES)
+def test_golden_cases(index):
+    c = load(f"neighborhood_case{index}")
+    spatial = tuple(int(x) for x in c["spatial"])
+    window = tuple(int(x) for x in c["window"])
+    q, k, v, dout = (c[n].cuda() for n in ("q", "k", "v", "dout"))
+    actual = run(q, k, v, dout, spatial, window, c["scale"])
+    gate(actual, q, k, v, dout, spatial, window, c["scale"])
+    tol = TOL[q.dtype]["norm"]
+    for name, got in zip(NAMES, actual):
+        want = c[f"exact_{name}"]
+        if float(want.abs().max()) > 0:
+            assert ao.per_head_relative_error(got.cpu(), want) < tol, name
+    if len(spatial) == 3:
+        assert ao.relative_error(actual[0].cpu(), c["two_term"]) < tol
+
+
+@pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16))
+@pytest.mark.parametrize("spatial,window", (((9, 11), (3, 5)), ((8, 8), (4, 6)), ((3, 7, 9), (3, 5, 5)),
+                                            ((2, 6, 5), (2, 2, 4)), ((1, 1, 70), (1, 1, 7))))
+def test_random_grids(spatial, window, dtype):
+    gen = torch.Generator().manual_seed(sum(spatial) * 7 + sum(window))
+    tokens = 1
+    for n in spatial:
+        tokens *= n
+    q, k, v, dout = (torch.randn(2, 3, tokens, 64, generator=gen).to(dtype).cuda() for _ in range(4))
+    for scale in (0.125, -0.125):
+        actual = run(q, k, v, dout, spatial, window, scale)
+        gate(actual, q, k, v, dout, spatial, window, scale)
+
+
+def test_shifted_border_counts_are_exact():
+    # 1x5 grid, window 3, zero scores: P = 1/3 everywhere, so dV counts how many queries see each key
+    q = torch.zeros(1, 1, 5, 64, device="cuda", dtype=torch.float16)
+    dout = torch.ones_like(q)
+    out, dq, dk, dv = run(q, q.clone(), torch.ones_like(q), dout, (1, 5), (1, 3), 0.125)
+    third = float(torch.tensor(1 / 3).half())
+    want = torch.tensor([2, 3, 5, 3, 2], dtype=torch.float32) * third
+    torch.testing.assert_close(dv[0, 0, :, 0].float().cpu(), want, atol=2e-3, rtol=2e-3)
+    assert float(dq.abs().max()) == 0 and float(dk.abs().max()) == 0
+
+
+def test_video_layout_adapter():
+    K = api()
+    gen = torch.Generator().manual_seed(9)
+    shape = (1, 3, 6, 5, 2, 64)
+    q, k, v, dout = (torch.randn(shape, generator=gen).half().cuda() for _ in range(4))
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    out = K.neighborhood_attention_3d(*leaves, (11, 3, 5), None, 0.125)  # 11-frame window clipped to 3
+    assert out.shape == shape
+    flat = [t.flatten(1, 3).transpose(1, 2) for t in (q, k, v)]
+    ref = K.neighborhood_attention(*flat, spatial_shape=(3, 6, 5), window_size=(3, 3, 5), scale=0.125)
+    torch.testing.assert_close(out, ref.transpose(1, 2).reshape(shape), atol=0, rtol=0)
+    grads = torch.autograd.grad(out, leaves, dout)
+    fl = [t.flatten(1, 3).transpose(1, 2) for t in (q, k, v, dout)]
+    actual = (ref, *[g.flatten(1, 3).transpose(1, 2) for g in grads])
+    gate(actual, *fl, (3, 6, 5), (3, 3, 5), 0.125)
+    for bad in (True, (False, True, False)):
+        with pytest.raises(ValueError, match="noncausal"):
+            K.neighborhood_attention_3d(q, k, v, 3, bad)
+    with pytest.raises(ValueError, match="window_size"):
+        K.neighborhood_attention(*flat, spatial_shape=(3, 6, 5), window_size=(4, 3, 5))
+
+
+def test_compiled_neighborhood_with_equal_length_different_geometry():
+    K = api()
+    gen = torch.Generator().manual_seed(10)
+    q, k, v = (torch.randn(1, 2, 60, 64, generator=gen).half().cuda() for _ in range(3))
+
+    def fn(q, k, v, spatial, window):
+        return K.neighborhood_attention(q, k, v, spatial_shape=spatial, window_size=window)
+
+    compiled = torch.compile(fn)
+    for spatial, window in (((6, 10), (3, 3)), ((10, 6), (3, 3)), ((3, 4, 5), (3, 3, 3))):
+        torch.testing.assert_close(compiled(q, k, v, spatial, window), fn(q, k, v, spatial, window), atol=0, rtol=0)
