@@ -138,6 +138,18 @@ KFA_API void kfa_clear_cache(void);
 KFA_API uint64_t kfa_launch_count(void);
 
 /*
+ * Per-kernel timing for benchmarks.  While enabled, every launch is bracketed by CUDA events
+ * on its own stream.  kfa_profile_collect() waits for the recorded events, adds them to
+ * per-kernel totals and returns the number of distinct kernels seen; kfa_profile_entry()
+ * reads one total; kfa_profile_reset() clears the totals.  Do not enable while capturing a
+ * CUDA graph.
+ */
+KFA_API void kfa_profile_enable(int on);
+KFA_API int kfa_profile_collect(void);
+KFA_API int kfa_profile_entry(int index, char* name, size_t name_bytes, double* total_ms, uint64_t* launches);
+KFA_API void kfa_profile_reset(void);
+
+/*
  * Device-side status: 0 when no kernel reported a problem, otherwise the code a bounded
  * wait stored when it gave up.  Reading does not synchronise; call after the stream is
  * idle.  `reset` != 0 clears it.

@@ -164,11 +164,12 @@ __global__ void __launch_bounds__(kWarps * 32) general_forward(AttnParams p) {
 }
 
 // -------------------------------------------------------------------- delta
-// delta[b,h,r] = sum_d f32(O) * f32(dO); one warp per row.
+// delta[b,h,r] = sum_d f32(O) * f32(dO); one thread per row, channels in ascending order with
+// fused multiply-adds.  The backward kernels below form dP = dO . V with the same chain, so for
+// a row whose output equals a value row (a single visible key) dP - delta is exactly zero.
 template <typename T>
 __global__ void __launch_bounds__(128) output_delta(AttnParams p) {
-    const int lane = threadIdx.x & 31;
-    const int64_t row_id = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int64_t row_id = (int64_t)blockIdx.x * 128 + threadIdx.x;
     const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
     if (row_id >= rows) return;
     const int r = (int)(row_id % p.Sq);
@@ -177,10 +178,9 @@ __global__ void __launch_bounds__(128) output_delta(AttnParams p) {
     const T* o = reinterpret_cast<const T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] + (int64_t)r * p.os[2];
     const T* g = reinterpret_cast<const T*>(p.dout) + (int64_t)b * p.gs[0] + (int64_t)h * p.gs[1] + (int64_t)r * p.gs[2];
     float sum = 0.f;
-    for (int d = lane; d < p.D; d += 32)
-        sum += to_float<T>(o[(int64_t)d * p.os[3]]) * to_float<T>(g[(int64_t)d * p.gs[3]]);
-    sum = warp_sum(sum);
-    if (lane == 0) p.delta[row_id] = sum;
+    for (int d = 0; d < p.D; ++d)
+        sum = fmaf(to_float<T>(g[(int64_t)d * p.gs[3]]), to_float<T>(o[(int64_t)d * p.os[3]]), sum);
+    p.delta[row_id] = sum;
 }
 
 // ------------------------------------------------------------ backward: dQ
@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(kWarps * 32) general_backward_q(AttnParams p) 
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         s[r] += myq[r * Dp + d + i] * kx[i];
-                        dp[r] += myg[r * Dp + d + i] * vx[i];
+                        dp[r] = fmaf(myg[r * Dp + d + i], vx[i], dp[r]);
                     }
                 }
             }
@@ -358,7 +358,7 @@ __global__ void __launch_bounds__(kWarps * 32) general_backward_kv(AttnParams p)
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             s[r] += myk[r * Dp + d + i] * qx[i];
-                            dp[r] += myv[r * Dp + d + i] * gx[i];
+                            dp[r] = fmaf(gx[i], myv[r * Dp + d + i], dp[r]);
                         }
                     }
                 }
@@ -531,15 +531,15 @@ cudaError_t launch_forward_t(const AttnParams& p, cudaStream_t st) {
 }
 
 template <typename T, bool VEC>
-cudaError_t launch_backward_t(const AttnParams& p, cudaStream_t st) {
+cudaError_t launch_backward_t(const AttnParams& p, int which, cudaStream_t st) {
     constexpr int R = 2;
     const int Dp = (p.D + 7) & ~7;
     const size_t smem = (size_t)kWarps * 2 * R * Dp * sizeof(float);
     const int64_t gq = blocks_for(p.Sq, kWarps * R) * p.B * p.Hq;
     const int64_t gk = blocks_for(p.Sk, kWarps * R) * p.B * p.Hkv;
-#define KFA_BWD(DI2)                                                                         \
-    general_backward_q<T, R, DI2, VEC><<<(unsigned)gq, kWarps * 32, smem, st>>>(p);          \
-    general_backward_kv<T, R, DI2, VEC><<<(unsigned)gk, kWarps * 32, smem, st>>>(p);
+#define KFA_BWD(DI2)                                                                                     \
+    if (which == 0) general_backward_q<T, R, DI2, VEC><<<(unsigned)gq, kWarps * 32, smem, st>>>(p);      \
+    else general_backward_kv<T, R, DI2, VEC><<<(unsigned)gk, kWarps * 32, smem, st>>>(p);
     if (p.D <= 64) { KFA_BWD(1) }
     else if (p.D <= 128) { KFA_BWD(2) }
     else if (p.D <= 256) { KFA_BWD(4) }
@@ -577,15 +577,18 @@ cudaError_t launch_general_forward(const AttnParams& p, bool bf16, cudaStream_t 
 
 cudaError_t launch_output_delta(const AttnParams& p, bool bf16, cudaStream_t st) {
     const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
-    if (bf16) output_delta<__nv_bfloat16><<<(unsigned)blocks_for(rows, 4), 128, 0, st>>>(p);
-    else output_delta<__half><<<(unsigned)blocks_for(rows, 4), 128, 0, st>>>(p);
+    if (bf16) output_delta<__nv_bfloat16><<<(unsigned)blocks_for(rows, 128), 128, 0, st>>>(p);
+    else output_delta<__half><<<(unsigned)blocks_for(rows, 128), 128, 0, st>>>(p);
     return cudaGetLastError();
 }
 
-cudaError_t launch_general_backward(const AttnParams& p, bool bf16, cudaStream_t st) {
+// which: 0 = query-gradient kernel, 1 = key/value-gradient kernel
+cudaError_t launch_general_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st) {
     const bool vec = general_vector_path(p, true);
-    if (bf16) return vec ? launch_backward_t<__nv_bfloat16, true>(p, st) : launch_backward_t<__nv_bfloat16, false>(p, st);
-    return vec ? launch_backward_t<__half, true>(p, st) : launch_backward_t<__half, false>(p, st);
+    if (bf16)
+        return vec ? launch_backward_t<__nv_bfloat16, true>(p, which, st)
+                   : launch_backward_t<__nv_bfloat16, false>(p, which, st);
+    return vec ? launch_backward_t<__half, true>(p, which, st) : launch_backward_t<__half, false>(p, which, st);
 }
 
 cudaError_t launch_center_keys(const void* k, void* out, float* mean, bool bf16, int B, int H, int S, int D,

@@ -9,6 +9,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 namespace {
 
@@ -24,6 +25,37 @@ int fail(int code, const char* fmt, ...) {
 }
 int cuda_fail(cudaError_t e, const char* what) {
     return fail(KFA_CUDA_ERROR, "%s: %s", what, cudaGetErrorString(e));
+}
+
+// Optional per-kernel timing with CUDA events on the launching stream.
+struct Sample {
+    const char* name;
+    cudaEvent_t begin, end;
+};
+std::mutex g_profile_mutex;
+std::atomic<bool> g_profile_on{false};
+std::vector<Sample> g_samples;
+struct Total {
+    const char* name;
+    double ms;
+    uint64_t launches;
+};
+std::vector<Total> g_totals;
+
+// Runs one launch; when profiling is on, brackets it with events.
+template <typename F>
+cudaError_t timed(const char* name, cudaStream_t st, F&& launch) {
+    g_launches += 1;
+    if (!g_profile_on.load(std::memory_order_relaxed)) return launch();
+    Sample s{name, nullptr, nullptr};
+    cudaEventCreate(&s.begin);
+    cudaEventCreate(&s.end);
+    cudaEventRecord(s.begin, st);
+    cudaError_t e = launch();
+    cudaEventRecord(s.end, st);
+    std::lock_guard<std::mutex> lock(g_profile_mutex);
+    g_samples.push_back(s);
+    return e;
 }
 
 // Per-device status word in mapped host memory: kernels write it only when a
@@ -212,6 +244,47 @@ int kfa_device_status(int reset) {
     return value;
 }
 
+void kfa_profile_enable(int on) {
+    std::lock_guard<std::mutex> lock(g_profile_mutex);
+    g_profile_on = on != 0;
+}
+
+int kfa_profile_collect(void) {
+    std::lock_guard<std::mutex> lock(g_profile_mutex);
+    for (Sample& s : g_samples) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(s.end) == cudaSuccess && cudaEventElapsedTime(&ms, s.begin, s.end) == cudaSuccess) {
+            bool found = false;
+            for (Total& t : g_totals)
+                if (std::strcmp(t.name, s.name) == 0) {
+                    t.ms += ms;
+                    t.launches += 1;
+                    found = true;
+                }
+            if (!found) g_totals.push_back(Total{s.name, ms, 1});
+        }
+        cudaEventDestroy(s.begin);
+        cudaEventDestroy(s.end);
+    }
+    g_samples.clear();
+    return (int)g_totals.size();
+}
+
+int kfa_profile_entry(int index, char* name, size_t name_bytes, double* total_ms, uint64_t* launches) {
+    std::lock_guard<std::mutex> lock(g_profile_mutex);
+    if (index < 0 || index >= (int)g_totals.size() || !name || name_bytes == 0)
+        return fail(KFA_INVALID_ARGUMENT, "profile entry %d does not exist", index);
+    std::snprintf(name, name_bytes, "%s", g_totals[index].name);
+    if (total_ms) *total_ms = g_totals[index].ms;
+    if (launches) *launches = g_totals[index].launches;
+    return 0;
+}
+
+void kfa_profile_reset(void) {
+    std::lock_guard<std::mutex> lock(g_profile_mutex);
+    g_totals.clear();
+}
+
 int kfa_selected_family(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
                         int causal, int backward) {
     if (check_qkv(q, k, v)) return -1;
@@ -253,18 +326,16 @@ int kfa_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, c
     if (p.has_mask) {
         int64_t n[4];
         block_extents(p, n);
-        ce = kfa::launch_pack_mask(p, (int)n[0], (int)n[1], (int)n[2], (int)n[3], st);
+        ce = timed("pack_mask", st, [&] { return kfa::launch_pack_mask(p, (int)n[0], (int)n[1], (int)n[2], (int)n[3], st); });
         if (ce != cudaSuccess) return cuda_fail(ce, "pack_mask launch");
-        g_launches += 1;
     }
     if (kfa::pipeline_forward_supported(p, bf16)) {
-        ce = kfa::launch_pipeline_forward(p, bf16, st);
+        ce = timed("pipeline_forward", st, [&] { return kfa::launch_pipeline_forward(p, bf16, st); });
         if (ce != cudaSuccess) return cuda_fail(ce, "pipeline forward launch");
     } else {
-        ce = kfa::launch_general_forward(p, bf16, st);
+        ce = timed("general_forward", st, [&] { return kfa::launch_general_forward(p, bf16, st); });
         if (ce != cudaSuccess) return cuda_fail(ce, "general forward launch");
     }
-    g_launches += 1;
     return 0;
 }
 
@@ -308,16 +379,19 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
     copy4(p.dvs, dv->strides);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool bf16 = q->dtype == KFA_BF16;
-    cudaError_t ce = kfa::launch_output_delta(p, bf16, st);
+    cudaError_t ce = timed("output_delta", st, [&] { return kfa::launch_output_delta(p, bf16, st); });
     if (ce != cudaSuccess) return cuda_fail(ce, "output_delta launch");
     if (kfa::pipeline_backward_supported(p, bf16)) {
-        ce = kfa::launch_pipeline_backward(p, bf16, st);
-        if (ce != cudaSuccess) return cuda_fail(ce, "pipeline backward launch");
+        ce = timed("pipeline_backward_q", st, [&] { return kfa::launch_pipeline_backward(p, bf16, 0, st); });
+        if (ce != cudaSuccess) return cuda_fail(ce, "pipeline backward (dQ) launch");
+        ce = timed("pipeline_backward_kv", st, [&] { return kfa::launch_pipeline_backward(p, bf16, 1, st); });
+        if (ce != cudaSuccess) return cuda_fail(ce, "pipeline backward (dK/dV) launch");
     } else {
-        ce = kfa::launch_general_backward(p, bf16, st);
-        if (ce != cudaSuccess) return cuda_fail(ce, "general backward launch");
+        ce = timed("general_backward_q", st, [&] { return kfa::launch_general_backward(p, bf16, 0, st); });
+        if (ce != cudaSuccess) return cuda_fail(ce, "general backward (dQ) launch");
+        ce = timed("general_backward_kv", st, [&] { return kfa::launch_general_backward(p, bf16, 1, st); });
+        if (ce != cudaSuccess) return cuda_fail(ce, "general backward (dK/dV) launch");
     }
-    g_launches += 3;
     return 0;
 }
 
@@ -335,12 +409,14 @@ int kfa_center_keys(const kfa_tensor* k, kfa_tensor* centered, void* workspace, 
     for (int i = 0; i < 4; ++i)
         if (k->sizes[i] <= 0 || k->sizes[i] > INT32_MAX) return fail(KFA_INVALID_ARGUMENT, "center_keys: bad extent");
     if (k->sizes[0] * k->sizes[1] > 65535) return fail(KFA_TOO_LARGE, "center_keys: batch*heads exceeds 65535");
-    cudaError_t ce = kfa::launch_center_keys(k->data, centered->data, static_cast<float*>(workspace),
-                                             k->dtype == KFA_BF16, (int)k->sizes[0], (int)k->sizes[1],
-                                             (int)k->sizes[2], (int)k->sizes[3], k->strides, centered->strides,
-                                             static_cast<cudaStream_t>(stream));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t ce = timed("center_keys", st, [&] {
+        return kfa::launch_center_keys(k->data, centered->data, static_cast<float*>(workspace), k->dtype == KFA_BF16,
+                                       (int)k->sizes[0], (int)k->sizes[1], (int)k->sizes[2], (int)k->sizes[3],
+                                       k->strides, centered->strides, st);
+    });
     if (ce != cudaSuccess) return cuda_fail(ce, "center_keys launch");
-    g_launches += 2;
+    g_launches += 1;  // two kernels per call
     return 0;
 }
 
@@ -359,9 +435,10 @@ int kfa_neighborhood_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa
     p.maximum = static_cast<float*>(maximum->data);
     p.logsum = static_cast<float*>(logsum->data);
     p.two_term = nd == 3 ? 1 : 0;
-    cudaError_t ce = kfa::launch_neighborhood_forward(p, q->dtype == KFA_BF16, static_cast<cudaStream_t>(stream));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t ce = timed("neighborhood_forward", st,
+                           [&] { return kfa::launch_neighborhood_forward(p, q->dtype == KFA_BF16, st); });
     if (ce != cudaSuccess) return cuda_fail(ce, "neighborhood forward launch");
-    g_launches += 1;
     return 0;
 }
 
@@ -405,11 +482,12 @@ int kfa_neighborhood_backward(const kfa_tensor* q, const kfa_tensor* k, const kf
     copy4(p.dvs, dv->strides);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool bf16 = q->dtype == KFA_BF16;
-    cudaError_t ce = kfa::launch_output_delta(p, bf16, st);
+    cudaError_t ce = timed("output_delta", st, [&] { return kfa::launch_output_delta(p, bf16, st); });
     if (ce != cudaSuccess) return cuda_fail(ce, "output_delta launch");
-    ce = kfa::launch_neighborhood_backward(p, bf16, st);
-    if (ce != cudaSuccess) return cuda_fail(ce, "neighborhood backward launch");
-    g_launches += 3;
+    ce = timed("neighborhood_backward_q", st, [&] { return kfa::launch_neighborhood_backward(p, bf16, 0, st); });
+    if (ce != cudaSuccess) return cuda_fail(ce, "neighborhood backward (dQ) launch");
+    ce = timed("neighborhood_backward_kv", st, [&] { return kfa::launch_neighborhood_backward(p, bf16, 1, st); });
+    if (ce != cudaSuccess) return cuda_fail(ce, "neighborhood backward (dK/dV) launch");
     return 0;
 }
 
@@ -426,13 +504,15 @@ int kfa_merge_partial(kfa_tensor* acc_out, kfa_tensor* acc_maximum, kfa_tensor* 
     if (!contiguous3(acc_maximum, B, H, S) || !contiguous3(acc_logsum, B, H, S) ||
         !contiguous3(part_maximum, B, H, S) || !contiguous3(part_logsum, B, H, S))
         return fail(KFA_INVALID_ARGUMENT, "merge statistics must be contiguous float32 [B,H,S]");
-    cudaError_t ce = kfa::launch_merge_partial(
-        static_cast<float*>(acc_out->data), static_cast<float*>(acc_maximum->data),
-        static_cast<float*>(acc_logsum->data), part_out->data, static_cast<const float*>(part_maximum->data),
-        static_cast<const float*>(part_logsum->data), part_out->dtype == KFA_BF16, (int)B, (int)H, (int)S, (int)D,
-        part_out->strides, scale, static_cast<cudaStream_t>(stream));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t ce = timed("merge_partial", st, [&] {
+        return kfa::launch_merge_partial(
+            static_cast<float*>(acc_out->data), static_cast<float*>(acc_maximum->data),
+            static_cast<float*>(acc_logsum->data), part_out->data, static_cast<const float*>(part_maximum->data),
+            static_cast<const float*>(part_logsum->data), part_out->dtype == KFA_BF16, (int)B, (int)H, (int)S, (int)D,
+            part_out->strides, scale, st);
+    });
     if (ce != cudaSuccess) return cuda_fail(ce, "merge launch");
-    g_launches += 1;
     return 0;
 }
 

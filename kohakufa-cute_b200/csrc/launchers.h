@@ -8,7 +8,7 @@ bool general_vector_path(const AttnParams& p, bool backward);
 cudaError_t launch_pack_mask(const AttnParams& p, int nb, int nh, int nq, int nk, cudaStream_t st);
 cudaError_t launch_general_forward(const AttnParams& p, bool bf16, cudaStream_t st);
 cudaError_t launch_output_delta(const AttnParams& p, bool bf16, cudaStream_t st);
-cudaError_t launch_general_backward(const AttnParams& p, bool bf16, cudaStream_t st);
+cudaError_t launch_general_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st);
 cudaError_t launch_center_keys(const void* k, void* out, float* mean, bool bf16, int B, int H, int S, int D,
                                const int64_t* ks, const int64_t* os, cudaStream_t st);
 cudaError_t launch_merge_partial(float* acc, float* am, float* al, const void* part, const float* pm, const float* pl,
@@ -16,14 +16,14 @@ cudaError_t launch_merge_partial(float* acc, float* am, float* al, const void* p
                                  cudaStream_t st);
 
 cudaError_t launch_neighborhood_forward(const AttnParams& p, bool bf16, cudaStream_t st);
-cudaError_t launch_neighborhood_backward(const AttnParams& p, bool bf16, cudaStream_t st);
+cudaError_t launch_neighborhood_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st);
 
 // Tensor-memory pipeline family (tcgen05).  `*_supported` says whether the
 // operands meet the family's layout requirements.
 bool pipeline_forward_supported(const AttnParams& p, bool bf16);
 cudaError_t launch_pipeline_forward(const AttnParams& p, bool bf16, cudaStream_t st);
 bool pipeline_backward_supported(const AttnParams& p, bool bf16);
-cudaError_t launch_pipeline_backward(const AttnParams& p, bool bf16, cudaStream_t st);
+cudaError_t launch_pipeline_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st);
 int pipeline_configured_variants();
 void pipeline_forget_variants();
 

@@ -245,15 +245,16 @@ cudaError_t forward_t(const AttnParams& p, cudaStream_t st) {
     return cudaGetLastError();
 }
 template <typename T>
-cudaError_t backward_t(const AttnParams& p, cudaStream_t st) {
+cudaError_t backward_t(const AttnParams& p, int which, cudaStream_t st) {
     const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
     const unsigned grid = (unsigned)((rows + 3) / 4);
-    if (general_vector_path(p, true)) {
-        na_backward_q<T, true><<<grid, 128, 0, st>>>(p);
-        na_backward_kv<T, true><<<grid, 128, 0, st>>>(p);
+    const bool vec = general_vector_path(p, true);
+    if (which == 0) {
+        if (vec) na_backward_q<T, true><<<grid, 128, 0, st>>>(p);
+        else na_backward_q<T, false><<<grid, 128, 0, st>>>(p);
     } else {
-        na_backward_q<T, false><<<grid, 128, 0, st>>>(p);
-        na_backward_kv<T, false><<<grid, 128, 0, st>>>(p);
+        if (vec) na_backward_kv<T, true><<<grid, 128, 0, st>>>(p);
+        else na_backward_kv<T, false><<<grid, 128, 0, st>>>(p);
     }
     return cudaGetLastError();
 }
@@ -263,8 +264,8 @@ cudaError_t backward_t(const AttnParams& p, cudaStream_t st) {
 cudaError_t launch_neighborhood_forward(const AttnParams& p, bool bf16, cudaStream_t st) {
     return bf16 ? forward_t<__nv_bfloat16>(p, st) : forward_t<__half>(p, st);
 }
-cudaError_t launch_neighborhood_backward(const AttnParams& p, bool bf16, cudaStream_t st) {
-    return bf16 ? backward_t<__nv_bfloat16>(p, st) : backward_t<__half>(p, st);
+cudaError_t launch_neighborhood_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st) {
+    return bf16 ? backward_t<__nv_bfloat16>(p, which, st) : backward_t<__half>(p, which, st);
 }
 
 }  // namespace kfa

@@ -12,7 +12,8 @@ bool pipeline_backward_supported(const AttnParams& p, bool bf16) {
     (void)bf16;
     return false;
 }
-cudaError_t launch_pipeline_backward(const AttnParams& p, bool bf16, cudaStream_t st) {
+cudaError_t launch_pipeline_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st) {
+    (void)which;
     (void)p;
     (void)bf16;
     (void)st;

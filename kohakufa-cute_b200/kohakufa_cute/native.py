@@ -62,6 +62,11 @@ SIGNATURES = {
     "kfa_clear_cache": (None, []),
     "kfa_launch_count": (ctypes.c_uint64, []),
     "kfa_device_status": (ctypes.c_int, [ctypes.c_int]),
+    "kfa_profile_enable": (None, [ctypes.c_int]),
+    "kfa_profile_collect": (ctypes.c_int, []),
+    "kfa_profile_entry": (ctypes.c_int, [ctypes.c_int, ctypes.c_char_p, ctypes.c_size_t,
+                                         ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_uint64)]),
+    "kfa_profile_reset": (None, []),
     "kfa_selected_family": (ctypes.c_int, [_TP, _TP, _TP, _TP, ctypes.c_int, ctypes.c_int]),
 }
 
@@ -250,3 +255,23 @@ def launch_count():
 
 def device_status(reset=False):
     return library().kfa_device_status(int(reset))
+
+
+def profile_enable(on=True):
+    """Bracket every kernel launch with CUDA events (benchmarks only; not during graph capture)."""
+    library().kfa_profile_enable(int(bool(on)))
+
+
+def profile_read(reset=True):
+    """{kernel name: (total milliseconds, launches)} accumulated since the last reset."""
+    lib = library()
+    count = lib.kfa_profile_collect()
+    result = {}
+    for index in range(count):
+        name = ctypes.create_string_buffer(64)
+        total, launches = ctypes.c_double(), ctypes.c_uint64()
+        _check(lib.kfa_profile_entry(index, name, 64, ctypes.byref(total), ctypes.byref(launches)))
+        result[name.value.decode()] = (total.value, launches.value)
+    if reset:
+        lib.kfa_profile_reset()
+    return result

@@ -44,7 +44,13 @@ def check_against_oracle(actual, q, k, v, dout, mask=None, causal=False, scale=N
         for reference, tag in ((want_exact, "fp64"), (want, "contract")):
             err = ao.per_head_relative_error(got, reference) if float(reference.abs().max()) > 0 else (
                 0.0 if float(got.abs().max()) == 0 else math.inf)
-            assert err < tol["norm"], f"{label}{name} vs {tag}: per-head relative error {err:.3e}"
+            limit = tol["norm"]
+            if tag == "fp64" and float(want_exact.abs().max()) > 0:
+                # On tiny heads the contract's own operand rounding can exceed the nominal gate; the
+                # requirement is then "no worse than the contract itself" (with 25 % slack).
+                own = ao.per_head_relative_error(want.to(dtype).double(), want_exact)
+                limit = max(limit, 1.25 * own)
+            assert err < limit, f"{label}{name} vs {tag}: per-head relative error {err:.3e} (limit {limit:.3e})"
         if not norm_only:
             torch.testing.assert_close(got.double(), want, atol=tol["elem"], rtol=tol["elem"],
                                        msg=lambda s: f"{label}{name} vs contract: {s}")
