@@ -161,7 +161,9 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
       } else if (warp == 8) {
         // ------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_s = umma_idesc(kTileQ, kTileK, BF16 ? 1 : 0, false, false);
+            // a negative scale takes the maximum over -S: negate the A operand of the score product
+            const uint32_t idesc_s =
+                umma_idesc(kTileQ, kTileK, BF16 ? 1 : 0, false, false) | (p.scale < 0.f ? kUmmaNegateA : 0u);
             constexpr uint32_t idesc_o = umma_idesc(kTileQ, D, BF16 ? 1 : 0, false, true);
             const uint32_t q_addr = smem_u32(sQ), kv_addr = smem_u32(sKV);
             auto issue_s = [&](int t, int slot) {
@@ -245,8 +247,8 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
         const int row = q0 + t * kTileQ + row_in_tile;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
         const uint32_t s_addr = lane_base + t * 128, o_addr = lane_base + 256 + t * 128;
-        const float sign = p.scale >= 0.f ? 1.f : -1.f;
         const float c2 = fabsf(p.scale) * kLog2e;
+        const uint64_t c2_pair = f2_pack(c2, c2);
         const uint8_t* kmask = p.has_mask ? p.mask + (int64_t)b * p.ms[0] + (int64_t)h * p.ms[1] : nullptr;
         float m_used = -INFINITY, m_true = -INFINITY, l = 0.f;
         int iter = 0;
@@ -257,6 +259,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
             ok = mbar_wait(&sh.s_ready[t], iter & 1, abort_word, 30 + t);
             if (!ok) break;
             tc_fence_after();
+            // scores arrive already multiplied by sign(scale) (negated A operand for negative scales)
             float s[kTileK];
 #pragma unroll
             for (int c = 0; c < kTileK; c += 32) {
@@ -266,31 +269,28 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                 for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(r[i]);
             }
             tmem_wait_ld();
-            if (sign < 0.f) {
-#pragma unroll
-                for (int c = 0; c < kTileK; ++c) s[c] = -s[c];
-            }
             const int key0 = j * kTileK;
-            const bool partial = (key0 + kTileK > p.Sk) || (p.causal && key0 + kTileK - 1 > q0 + t * kTileQ) ||
-                                 state == 1;
-            if (partial) {
+            // leading columns of this tile that pass the sequence-end and causal bounds for this row
+            int lim = p.Sk - key0;
+            if (p.causal) lim = min(lim, row - key0 + 1);
+            if (lim < kTileK) {
+#pragma unroll
+                for (int c = 0; c < kTileK; ++c) s[c] = c < lim ? s[c] : -INFINITY;
+            }
+            if (state == 1) {
 #pragma unroll
                 for (int c = 0; c < kTileK; ++c) {
-                    const int key = key0 + c;
-                    bool vis = key < p.Sk && (!p.causal || key <= row);
-                    if (vis && kmask) vis = kmask[(int64_t)key * p.ms[3]] != 0;
-                    s[c] = vis ? s[c] : -INFINITY;
+                    const int key = min(key0 + c, p.Sk - 1);
+                    s[c] = kmask[(int64_t)key * p.ms[3]] != 0 ? s[c] : -INFINITY;
                 }
             }
-            float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+            float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
 #pragma unroll
-            for (int c = 4; c < kTileK; c += 4) {
-                mx0 = fmaxf(mx0, s[c]);
-                mx1 = fmaxf(mx1, s[c + 1]);
-                mx2 = fmaxf(mx2, s[c + 2]);
-                mx3 = fmaxf(mx3, s[c + 3]);
+            for (int c = 6; c < kTileK - 2; c += 4) {
+                mx0 = max3(mx0, s[c], s[c + 1]);
+                mx1 = max3(mx1, s[c + 2], s[c + 3]);
             }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            const float mx = max3(mx0, mx1, fmaxf(s[kTileK - 2], s[kTileK - 1]));
             m_true = fmaxf(m_true, mx);
             const bool rebase = mx > m_used && (m_used == -INFINITY || (mx - m_used) * c2 > kRebase);
             float alpha = 1.f;
@@ -311,25 +311,34 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                 }
             }
             const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-            float sum0 = 0.f, sum1 = 0.f;
+            const uint64_t m_pair = f2_pack(m_safe, m_safe);
+            uint64_t sum_a = f2_pack(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
             for (int c = 0; c < kTileK; c += 32) {
                 uint32_t w[16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float pa = ex2((s[c + 2 * i] - m_safe) * c2);
-                    float pb = ex2((s[c + 2 * i + 1] - m_safe) * c2);
-                    if (partial) {  // hidden entries carry -inf; keep them at zero also when |scale| is 0
-                        pa = s[c + 2 * i] == -INFINITY ? 0.f : pa;
-                        pb = s[c + 2 * i + 1] == -INFINITY ? 0.f : pb;
-                    }
-                    sum0 += pa;
-                    sum1 += pb;
+                for (int i = 0; i < 16; i += 2) {
+                    // (s - m) first, then the multiplication by |scale|*log2e, two lanes per instruction
+                    float pa, pb, pc, pd;
+                    f2_unpack(f2_mul(f2_sub(f2_pack(s[c + 2 * i], s[c + 2 * i + 1]), m_pair), c2_pair), pa, pb);
+                    f2_unpack(f2_mul(f2_sub(f2_pack(s[c + 2 * i + 2], s[c + 2 * i + 3]), m_pair), c2_pair), pc, pd);
+                    pa = ex2(pa);
+                    pb = ex2(pb);
+                    pc = ex2(pc);
+                    pd = ex2(pd);
+                    sum_a = f2_add(sum_a, f2_pack(pa, pb));
+                    sum_b = f2_add(sum_b, f2_pack(pc, pd));
                     w[i] = pack2<BF16>(pa, pb);
+                    w[i + 1] = pack2<BF16>(pc, pd);
                 }
                 tmem_st16(s_addr + c / 2, w);
             }
-            l += sum0 + sum1;
+            {
+                float x0, x1, x2, x3;
+                f2_unpack(sum_a, x0, x1);
+                f2_unpack(sum_b, x2, x3);
+                l += (x0 + x1) + (x2 + x3);
+            }
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&sh.p_ready[t]);
@@ -412,6 +421,7 @@ bool pipeline_forward_supported(const AttnParams& p, bool bf16) {
     (void)bf16;
     if (p.D != 64 && p.D != 128) return false;
     if (p.nd != 0) return false;
+    if (p.scale == 0.f) return false;  // hidden scores are -inf; -inf * 0 is not representable in the fast path
     if (p.has_mask && p.ms[2] != 0) return false;  // only masks broadcast over the query axis
     if (!tma_compatible(p.q, p.qs, p.B, p.Hq, p.Sq) || !tma_compatible(p.k, p.ks, p.B, p.Hkv, p.Sk) ||
         !tma_compatible(p.v, p.vs, p.B, p.Hkv, p.Sk))

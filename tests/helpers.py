@@ -37,7 +37,12 @@ def check_against_oracle(actual, q, k, v, dout, mask=None, causal=False, scale=N
     g = dout.detach().cpu()
     m = None if mask is None else mask.detach().cpu()
     exact = ao.math_reference(cpu, g, m, causal, scale)
-    contract = ao.contract_reference(cpu, g, m, causal, scale, output=actual[0].detach().cpu())
+    if k.shape[2] == 1:
+        # A visible single key has P = 1 and dS = 0 exactly; two independent FP32 reductions of dP and
+        # delta in the contract would invent a few-ulp gradient and reject the kernel's exact zero.
+        contract = exact
+    else:
+        contract = ao.contract_reference(cpu, g, m, causal, scale, output=actual[0].detach().cpu())
     for name, got, want_exact, want in zip(NAMES, actual, exact, contract):
         got = got.detach().cpu()
         assert bool(torch.isfinite(got).all()), f"{label}{name}: non-finite values"
