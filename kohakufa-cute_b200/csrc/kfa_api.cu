@@ -379,9 +379,12 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
     copy4(p.dvs, dv->strides);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool bf16 = q->dtype == KFA_BF16;
-    cudaError_t ce = timed("output_delta", st, [&] { return kfa::launch_output_delta(p, bf16, st); });
+    const bool pipeline = kfa::pipeline_backward_supported(p, bf16);
+    cudaError_t ce = timed("output_delta", st, [&] {
+        return pipeline ? kfa::launch_pipeline_delta(p, bf16, st) : kfa::launch_output_delta(p, bf16, st);
+    });
     if (ce != cudaSuccess) return cuda_fail(ce, "output_delta launch");
-    if (kfa::pipeline_backward_supported(p, bf16)) {
+    if (pipeline) {
         ce = timed("pipeline_backward_q", st, [&] { return kfa::launch_pipeline_backward(p, bf16, 0, st); });
         if (ce != cudaSuccess) return cuda_fail(ce, "pipeline backward (dQ) launch");
         ce = timed("pipeline_backward_kv", st, [&] { return kfa::launch_pipeline_backward(p, bf16, 1, st); });

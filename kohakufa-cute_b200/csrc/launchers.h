@@ -24,6 +24,7 @@ bool pipeline_forward_supported(const AttnParams& p, bool bf16);
 cudaError_t launch_pipeline_forward(const AttnParams& p, bool bf16, cudaStream_t st);
 bool pipeline_backward_supported(const AttnParams& p, bool bf16);
 cudaError_t launch_pipeline_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st);
+cudaError_t launch_pipeline_delta(const AttnParams& p, bool bf16, cudaStream_t st);
 int pipeline_configured_variants();
 void pipeline_forget_variants();
 

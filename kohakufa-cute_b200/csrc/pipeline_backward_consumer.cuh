@@ -1,0 +1,198 @@
+// Consumer warpgroups of the backward pipeline: scores -> P -> dS, and the gradient epilogue.
+//
+// A consumer thread owns one owner row (tensor-memory lane) and the 64 columns of its
+// warpgroup's sub-tile.  Per element, in FP32:
+//   P      = ex2((s' - m) * |scale| * log2e - logsum)      s' arrives already sign-adjusted
+//   P_low  = round(P)                                       one rounding to the input type
+//   dS_low = round(P_low * (dP - delta))
+// m, logsum and delta belong to the query: the row for query owners (registers), the column for
+// key owners (staged in shared memory).  Hidden entries get P = 0.
+#pragma once
+#include "pipeline_backward_roles.cuh"
+
+namespace kfa {
+namespace bwd {
+
+template <int D, bool BF16, bool KV>
+__device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV>& w, Shared& sh, uint32_t tmem,
+                                              const float* s_stats, int wg, int warp, int lane) {
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    volatile int* abort_word = &sh.abort_word;
+    const int r = (warp & 3) * 32 + lane;  // owner row inside the tile == tensor-memory lane
+    const int owner_row = w.owner0 + r;
+    const int owner_len = KV ? p.Sk : p.Sq;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const uint32_t s_addr = lane_base + wg * 128, dp_addr = s_addr + 64;
+    const float c2 = fabsf(p.scale) * kLog2e;
+    const uint64_t c2_pair = f2_pack(c2, c2);
+
+    // per-row quantities
+    float row_m = INFINITY, row_ls = 0.f, row_dl = 0.f;
+    bool row_ok = owner_row < owner_len;
+    const uint8_t* kmask = p.has_mask ? p.mask + (int64_t)w.b * p.ms[0] : nullptr;  // broadcast over heads, queries
+    if (KV) {
+        if (row_ok && kmask) row_ok = kmask[(int64_t)owner_row * p.ms[3]] != 0;
+    } else if (row_ok) {
+        const int64_t si = ((int64_t)w.b * p.Hq + w.head) * p.Sq + owner_row;
+        row_m = p.maximum[si];
+        row_ls = p.logsum[si];
+        row_dl = p.delta[si];
+        if (row_m == -INFINITY) row_m = INFINITY;  // nothing visible: every P is zero
+    }
+
+    int g, i;
+    w.begin(p, g, i);
+    int unit = 0;
+    bool ok = true;
+    while (w.valid(g) && ok) {
+        if (KV) ok = mbar_wait(&sh.stats_full[unit & 1], (unit >> 1) & 1, abort_word, 140);
+        if (ok) ok = mbar_wait(&sh.sdp_ready[wg], unit & 1, abort_word, 141 + wg);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t s[kSub], dp[kSub];
+        {
+            uint32_t a[32], b2[32];
+            tmem_ld32(s_addr, a);
+            tmem_ld32(s_addr + 32, b2);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                s[c] = a[c];
+                s[32 + c] = b2[c];
+            }
+            tmem_ld32(dp_addr, a);
+            tmem_ld32(dp_addr + 32, b2);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                dp[c] = a[c];
+                dp[32 + c] = b2[c];
+            }
+        }
+        tmem_wait_ld();
+
+        // visibility of the 64 columns of this sub-tile: columns [lo, hi) of this row are visible
+        const int col0 = i * kTile + wg * kSub;  // first streamed row (key or query) of the sub-tile
+        int lo = 0, hi = kSub;
+        int state = 2;
+        if (KV) {
+            if (p.causal) lo = owner_row - col0;  // query index must be >= key index
+            if (!row_ok) lo = kSub;
+        } else {
+            hi = p.Sk - col0;
+            if (p.causal) hi = min(hi, owner_row - col0 + 1);
+            state = key_tile_state(p, w.b, w.head, i);
+        }
+        const bool clip = __any_sync(0xffffffffu, lo > 0 || hi < kSub);
+        const float* st = s_stats + (unit & 1) * 3 * kTile + wg * kSub;
+
+        uint32_t pw[kSub / 2], dw[kSub / 2];
+#pragma unroll
+        for (int c = 0; c < kSub; c += 2) {
+            uint64_t m2, ls2, dl2;
+            if (KV) {
+                const float2 mm = *reinterpret_cast<const float2*>(st + c);
+                const float2 ll = *reinterpret_cast<const float2*>(st + kTile + c);
+                const float2 dd = *reinterpret_cast<const float2*>(st + 2 * kTile + c);
+                m2 = f2_pack(mm.x, mm.y);
+                ls2 = f2_pack(ll.x, ll.y);
+                dl2 = f2_pack(dd.x, dd.y);
+            } else {
+                m2 = f2_pack(row_m, row_m);
+                ls2 = f2_pack(row_ls, row_ls);
+                dl2 = f2_pack(row_dl, row_dl);
+            }
+            const uint64_t s2 = f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+            float ea, eb;
+            f2_unpack(f2_sub(f2_mul(f2_sub(s2, m2), c2_pair), ls2), ea, eb);
+            float pa = ex2(ea), pb = ex2(eb);
+            if (clip) {
+                pa = (c >= lo && c < hi) ? pa : 0.f;
+                pb = (c + 1 >= lo && c + 1 < hi) ? pb : 0.f;
+            }
+            if (!KV && state == 1) {
+                pa = kmask[(int64_t)min(col0 + c, p.Sk - 1) * p.ms[3]] != 0 ? pa : 0.f;
+                pb = kmask[(int64_t)min(col0 + c + 1, p.Sk - 1) * p.ms[3]] != 0 ? pb : 0.f;
+            }
+            const uint32_t packed = pack2<BF16>(pa, pb);
+            pw[c / 2] = packed;
+            const float2 pl = unpack2<BF16>(packed);
+            const uint64_t res = f2_sub(f2_pack(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), dl2);
+            float da, db;
+            f2_unpack(f2_mul(f2_pack(pl.x, pl.y), res), da, db);
+            dw[c / 2] = pack2<BF16>(da, db);
+        }
+        // P_low over the head of the S buffer (only key owners use it), dS_low over the head of dP
+        if (KV) {
+            uint32_t (&half0)[16] = *reinterpret_cast<uint32_t(*)[16]>(&pw[0]);
+            uint32_t (&half1)[16] = *reinterpret_cast<uint32_t(*)[16]>(&pw[16]);
+            tmem_st16(s_addr, half0);
+            tmem_st16(s_addr + 16, half1);
+        }
+        {
+            uint32_t (&half0)[16] = *reinterpret_cast<uint32_t(*)[16]>(&dw[0]);
+            uint32_t (&half1)[16] = *reinterpret_cast<uint32_t(*)[16]>(&dw[16]);
+            tmem_st16(dp_addr, half0);
+            tmem_st16(dp_addr + 16, half1);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&sh.done[wg]);
+        if (KV) mbar_arrive(&sh.stats_empty[unit & 1]);
+        w.next(p, g, i);
+        ++unit;
+    }
+
+    // ---------------------------------------------------------------- epilogue
+    // Each warpgroup stores half of the channels of every gradient row.
+    constexpr int kHalf = D / 2;
+    const int ch0 = wg * kHalf;
+    T* out1 = nullptr;  // dQ or dK (scaled)
+    T* out2 = nullptr;  // dV
+    if (owner_row < owner_len) {
+        if (KV) {
+            out1 = reinterpret_cast<T*>(p.dk) + (int64_t)w.b * p.dks[0] + (int64_t)w.head * p.dks[1] +
+                   (int64_t)owner_row * p.dks[2] + ch0;
+            out2 = reinterpret_cast<T*>(p.dv) + (int64_t)w.b * p.dvs[0] + (int64_t)w.head * p.dvs[1] +
+                   (int64_t)owner_row * p.dvs[2] + ch0;
+        } else {
+            out1 = reinterpret_cast<T*>(p.dq) + (int64_t)w.b * p.dqs[0] + (int64_t)w.head * p.dqs[1] +
+                   (int64_t)owner_row * p.dqs[2] + ch0;
+        }
+    }
+    if (unit == 0) {
+        // no visible work for this owner tile: the gradients are exactly zero
+        if (ok && out1)
+            for (int d = 0; d < kHalf; d += 8) *reinterpret_cast<uint4*>(out1 + d) = make_uint4(0, 0, 0, 0);
+        if (ok && out2)
+            for (int d = 0; d < kHalf; d += 8) *reinterpret_cast<uint4*>(out2 + d) = make_uint4(0, 0, 0, 0);
+        return;
+    }
+    if (ok) ok = mbar_wait(&sh.final_done, 0, abort_word, 150);
+    if (!ok) return;
+    tc_fence_after();
+#pragma unroll
+    for (int which = 0; which < (KV ? 2 : 1); ++which) {
+        const uint32_t acc = lane_base + (which == 0 ? 384 : 256) + ch0;
+        T* out = which == 0 ? out1 : out2;
+        const float mul = which == 0 ? p.scale : 1.f;
+#pragma unroll
+        for (int c = 0; c < kHalf; c += 32) {
+            uint32_t v[32];
+            tmem_ld32(acc + c, v);
+            tmem_wait_ld();
+            if (out) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 8) {
+                    uint4 o;
+                    o.x = pack2<BF16>(__uint_as_float(v[e]) * mul, __uint_as_float(v[e + 1]) * mul);
+                    o.y = pack2<BF16>(__uint_as_float(v[e + 2]) * mul, __uint_as_float(v[e + 3]) * mul);
+                    o.z = pack2<BF16>(__uint_as_float(v[e + 4]) * mul, __uint_as_float(v[e + 5]) * mul);
+                    o.w = pack2<BF16>(__uint_as_float(v[e + 6]) * mul, __uint_as_float(v[e + 7]) * mul);
+                    *reinterpret_cast<uint4*>(out + c + e) = o;
+                }
+            }
+        }
+    }
+}
+
+}  // namespace bwd
+}  // namespace kfa

@@ -1,0 +1,284 @@
+// Backward pass on the tensor-memory pipeline: shared context, work iteration, and the
+// loader / MMA-issuer / statistics roles.  The consumer role is in
+// pipeline_backward_consumer.cuh and the kernel itself in pipeline_backward.cu.
+//
+// One kernel template serves both gradient owners:
+//   KV = false  a CTA owns 128 query rows of one (batch, query head) and streams key tiles;
+//               it produces dQ = (sum dS_low K) * scale.
+//   KV = true   a CTA owns 128 key rows of one (batch, K/V head) and streams the query tiles of
+//               every query head in the group; it produces dK = (sum dS_low^T Q) * scale and
+//               dV = sum P_low^T dO.  One owner per output row, so no atomics are needed.
+// Each streamed 128-row tile is processed as two 64-wide sub-tiles that ping-pong between two
+// consumer warpgroups: while one warpgroup turns scores into P and dS, the tensor core works on
+// the other sub-tile.  Per sub-tile the tensor core runs
+//   S  = A1 x B1^T   (A1 = owner operand 1: Q or K;  B1 = streamed operand 1: K or Q)
+//   dP = A2 x B2^T   (A2 = owner operand 2: dO or V; B2 = streamed operand 2: V or dO)
+//   grad1 += dS_low x B1      (dQ, or dK)          A operand read from tensor memory
+//   grad2 += P_low  x B2      (dV; KV only)        A operand read from tensor memory
+// Tensor memory (512 columns): [S_0 | dP_0 | S_1 | dP_1] 64 columns each, grad2 at 256, grad1 at
+// 384.  The 16-bit P and dS overwrite the first 32 columns of their own S / dP buffer.
+// (Reference behaviour: src/kohakufa_cute/blackwell_pipeline.py:610-662, 1279-1306 of the
+// reference project; arithmetic contract docs/precision.md:13-23.)
+#pragma once
+#include "kfa_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace kfa {
+namespace bwd {
+
+constexpr int kTile = 128;     // owner rows, and rows of a streamed tile
+constexpr int kSub = 64;       // columns of one sub-tile
+constexpr int kThreads = 384;  // consumer WG 0, consumer WG 1, (MMA, loader, statistics, idle)
+constexpr int kMaxPairs = 4;
+
+template <int D>
+struct Cfg {
+    static constexpr int kChunks = D / 64;
+    static constexpr int kTileBytes = kTile * D * 2;
+    static constexpr int kPairs = D == 128 ? 2 : 4;  // ring slots, each holds both streamed operands
+    static constexpr int kStatsBytes = 2 * 3 * kTile * 4;
+    static constexpr int kSmemBytes = 2 * kTileBytes + kPairs * 2 * kTileBytes + kStatsBytes + 1024 + 256;
+};
+
+struct Maps {
+    CUtensorMap q, k, v, g;  // g = dO
+};
+
+struct Shared {
+    uint64_t owner_full;
+    uint64_t pair_full[kMaxPairs];
+    uint64_t pair_empty[kMaxPairs];
+    uint64_t sdp_ready[2];
+    uint64_t done[2];
+    uint64_t stats_full[2];
+    uint64_t stats_empty[2];
+    uint64_t final_done;
+    uint32_t tmem_base;
+    int abort_word;
+};
+
+// Combined state of a 128-key tile from the 64-key table entries: 0 hidden, 2 visible, 1 mixed.
+__device__ __forceinline__ int key_tile_state(const AttnParams& p, int b, int h, int j) {
+    if (!p.has_mask) return 2;
+    const int nk64 = (p.Sk + 63) >> 6;
+    const int32_t* base = p.blocks + (int64_t)b * p.bs[0] + (int64_t)h * p.bs[1];
+    const int s0 = base[(int64_t)(2 * j) * p.bs[3]];
+    const int s1 = (2 * j + 1 < nk64) ? base[(int64_t)(2 * j + 1) * p.bs[3]] : s0;
+    if (s0 == 0 && s1 == 0) return 0;
+    if (s0 == 2 && s1 == 2) return 2;
+    return 1;
+}
+
+// The CTA's place in the problem and its stream of work units.
+template <bool KV>
+struct Work {
+    int b, head, owner0;  // batch, owner head (query head or K/V head), first owner row
+    int first, end;       // streamed tile range [first, end)
+    int groups;           // query heads per owner (KV) or 1
+
+    __device__ __forceinline__ void init(const AttnParams& p) {
+        const int owner_len = KV ? p.Sk : p.Sq;
+        const int heads = KV ? p.Hkv : p.Hq;
+        const int nblk = (owner_len + kTile - 1) / kTile;
+        int blk = (int)(blockIdx.x % nblk);
+        if (!KV) blk = nblk - 1 - blk;  // causal: late query tiles carry the most work, start them first
+        const int64_t bh = blockIdx.x / nblk;
+        head = (int)(bh % heads);
+        b = (int)(bh / heads);
+        owner0 = blk * kTile;
+        if (KV) {
+            groups = p.group;
+            first = p.causal ? owner0 / kTile : 0;  // only queries r >= key see the key
+            end = (p.Sq + kTile - 1) / kTile;
+            if (key_tile_state(p, b, head * p.group, blk) == 0) end = first;  // every key of the tile is hidden
+        } else {
+            groups = 1;
+            first = 0;
+            const int row_hi = min(p.Sq, owner0 + kTile);
+            const int k_hi = p.causal ? min(p.Sk, row_hi) : p.Sk;
+            end = (k_hi + kTile - 1) / kTile;
+        }
+    }
+    // Unit cursor: (g, i).  Query owners skip key tiles the mask table marks hidden.
+    __device__ __forceinline__ bool live(const AttnParams& p, int i) const {
+        return KV || key_tile_state(p, b, head, i) != 0;
+    }
+    __device__ __forceinline__ void begin(const AttnParams& p, int& g, int& i) const {
+        g = 0;
+        i = first;
+        while (i < end && !live(p, i)) ++i;
+        if (i >= end) g = groups;
+    }
+    __device__ __forceinline__ void next(const AttnParams& p, int& g, int& i) const {
+        ++i;
+        while (i < end && !live(p, i)) ++i;
+        if (i >= end) {
+            ++g;
+            i = first;
+            if (!KV) g = groups;
+        }
+    }
+    __device__ __forceinline__ bool valid(int g) const { return g < groups; }
+    __device__ __forceinline__ int query_head(int g) const { return KV ? head * groups + g : head; }
+};
+
+template <int D, bool KV>
+__device__ __forceinline__ void loader_role(const Maps& maps, const AttnParams& p, const Work<KV>& w, Shared& sh,
+                                            uint8_t* s_owner, uint8_t* s_ring) {
+    using C = Cfg<D>;
+    volatile int* abort_word = &sh.abort_word;
+    int g, i;
+    w.begin(p, g, i);
+    if (!w.valid(g)) return;
+    const int kvh = KV ? w.head : w.head / p.group;
+    // owner operands: (K, V) for key owners, (Q, dO) for query owners
+    const CUtensorMap* own1 = KV ? &maps.k : &maps.q;
+    const CUtensorMap* own2 = KV ? &maps.v : &maps.g;
+    tma_prefetch_desc(own1);
+    tma_prefetch_desc(own2);
+    mbar_expect_tx(&sh.owner_full, 2 * C::kTileBytes);
+    for (int c = 0; c < C::kChunks; ++c) {
+        tma_load_4d(s_owner + c * (kTile * 128), own1, &sh.owner_full, c * 64, w.owner0, w.head, w.b);
+        tma_load_4d(s_owner + C::kTileBytes + c * (kTile * 128), own2, &sh.owner_full, c * 64, w.owner0, w.head, w.b);
+    }
+    const CUtensorMap* st1 = KV ? &maps.q : &maps.k;
+    const CUtensorMap* st2 = KV ? &maps.g : &maps.v;
+    int unit = 0;
+    bool ok = true;
+    while (w.valid(g) && ok) {
+        const int slot = unit % C::kPairs, round = unit / C::kPairs;
+        if (round > 0) ok = mbar_wait(&sh.pair_empty[slot], (round - 1) & 1, abort_word, 110);
+        if (!ok) break;
+        const int head = KV ? w.query_head(g) : kvh;
+        uint8_t* dst = s_ring + slot * 2 * C::kTileBytes;
+        mbar_expect_tx(&sh.pair_full[slot], 2 * C::kTileBytes);
+        for (int c = 0; c < C::kChunks; ++c) {
+            tma_load_4d(dst + c * (kTile * 128), st1, &sh.pair_full[slot], c * 64, i * kTile, head, w.b);
+            tma_load_4d(dst + C::kTileBytes + c * (kTile * 128), st2, &sh.pair_full[slot], c * 64, i * kTile, head,
+                        w.b);
+        }
+        w.next(p, g, i);
+        ++unit;
+    }
+}
+
+template <int D, bool BF16, bool KV>
+__device__ __forceinline__ void mma_role(const AttnParams& p, const Work<KV>& w, Shared& sh, uint32_t tmem,
+                                         uint8_t* s_owner, uint8_t* s_ring) {
+    using C = Cfg<D>;
+    volatile int* abort_word = &sh.abort_word;
+    int g, i;
+    w.begin(p, g, i);
+    if (!w.valid(g)) return;
+    // A negative scale takes maxima over -S: the forward saved statistics of -S, so negate operand A.
+    const uint32_t idesc_s = umma_idesc(kTile, kSub, BF16 ? 1 : 0, false, false) | (p.scale < 0.f ? kUmmaNegateA : 0u);
+    constexpr uint32_t idesc_p = umma_idesc(kTile, kSub, BF16 ? 1 : 0, false, false);
+    constexpr uint32_t idesc_g = umma_idesc(kTile, D, BF16 ? 1 : 0, false, true);
+    const uint32_t own1 = smem_u32(s_owner), own2 = own1 + C::kTileBytes, ring = smem_u32(s_ring);
+
+    // S_b and dP_b of sub-tile `sub` of the pair in `slot`
+    auto issue_scores = [&](int slot, int sub) {
+        const uint32_t st1 = ring + slot * 2 * C::kTileBytes, st2 = st1 + C::kTileBytes;
+        const uint32_t s_col = tmem + sub * 128, dp_col = s_col + 64;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk / 4) * (kTile * 128) + (kk % 4) * 32;
+            umma_ss(s_col, umma_desc_sw128(own1 + off, 16, 1024), umma_desc_sw128(st1 + sub * 8192 + off, 16, 1024),
+                    idesc_s, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk / 4) * (kTile * 128) + (kk % 4) * 32;
+            umma_ss(dp_col, umma_desc_sw128(own2 + off, 16, 1024), umma_desc_sw128(st2 + sub * 8192 + off, 16, 1024),
+                    idesc_p, kk > 0);
+        }
+        umma_commit(&sh.sdp_ready[sub]);
+    };
+    // gradient accumulation of sub-tile `sub`: A operands are the packed P / dS in tensor memory
+    auto issue_grads = [&](int slot, int sub, bool accumulate) {
+        const uint32_t st1 = ring + slot * 2 * C::kTileBytes, st2 = st1 + C::kTileBytes;
+        const uint32_t p_col = tmem + sub * 128, ds_col = p_col + 64;
+#pragma unroll
+        for (int kk = 0; kk < kSub / 16; ++kk) {
+            const uint32_t rows = (sub * 4 + kk) * 2048;  // 16 streamed rows per step, 128 bytes each
+            if (KV)
+                umma_ts(tmem + 256, p_col + kk * 8, umma_desc_sw128(st2 + rows, kTile * 128, 1024), idesc_g,
+                        accumulate || kk > 0);
+            umma_ts(tmem + 384, ds_col + kk * 8, umma_desc_sw128(st1 + rows, kTile * 128, 1024), idesc_g,
+                    accumulate || kk > 0);
+        }
+    };
+
+    bool ok = mbar_wait(&sh.owner_full, 0, abort_word, 120);
+    if (ok) ok = mbar_wait(&sh.pair_full[0], 0, abort_word, 121);
+    if (!ok) return;
+    tc_fence_after();
+    issue_scores(0, 0);
+    issue_scores(0, 1);
+    int unit = 0;
+    while (w.valid(g) && ok) {
+        int gn = g, in = i;
+        w.next(p, gn, in);
+        const bool more = w.valid(gn);
+        const int slot = unit % C::kPairs, nslot = (unit + 1) % C::kPairs;
+        for (int sub = 0; sub < 2 && ok; ++sub) {
+            ok = mbar_wait(&sh.done[sub], unit & 1, abort_word, 122 + sub);
+            if (!ok) break;
+            tc_fence_after();
+            issue_grads(slot, sub, unit > 0 || sub > 0);
+            if (sub == 1) umma_commit(&sh.pair_empty[slot]);
+            if (more) {
+                if (sub == 0) {
+                    ok = mbar_wait(&sh.pair_full[nslot], ((unit + 1) / C::kPairs) & 1, abort_word, 124);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                issue_scores(nslot, sub);
+            }
+        }
+        g = gn;
+        i = in;
+        ++unit;
+    }
+    if (ok) umma_commit(&sh.final_done);
+}
+
+// Key owners need the three row statistics of every streamed query: one warp stages them.
+// A query beyond the sequence end, or one that saw no key in the forward pass (maximum = -inf),
+// gets maximum = +inf so that its probabilities evaluate to exactly zero.
+template <bool KV>
+__device__ __forceinline__ void stats_role(const AttnParams& p, const Work<KV>& w, Shared& sh, float* s_stats,
+                                           int lane) {
+    volatile int* abort_word = &sh.abort_word;
+    int g, i;
+    w.begin(p, g, i);
+    int unit = 0;
+    bool ok = true;
+    while (w.valid(g) && ok) {
+        const int buf = unit & 1;
+        if (unit >= 2) ok = mbar_wait(&sh.stats_empty[buf], ((unit >> 1) - 1) & 1, abort_word, 130);
+        if (!ok) break;
+        const int64_t base = ((int64_t)w.b * p.Hq + w.query_head(g)) * p.Sq;
+        float* dst = s_stats + buf * 3 * kTile;
+        for (int c = lane; c < kTile; c += 32) {
+            const int row = i * kTile + c;
+            float m = INFINITY, ls = 0.f, dl = 0.f;
+            if (row < p.Sq) {
+                m = p.maximum[base + row];
+                ls = p.logsum[base + row];
+                dl = p.delta[base + row];
+                if (m == -INFINITY) m = INFINITY;
+            }
+            dst[c] = m;
+            dst[kTile + c] = ls;
+            dst[2 * kTile + c] = dl;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.stats_full[buf]);
+        w.next(p, g, i);
+        ++unit;
+    }
+}
+
+}  // namespace bwd
+}  // namespace kfa

@@ -421,7 +421,7 @@ bool pipeline_forward_supported(const AttnParams& p, bool bf16) {
     (void)bf16;
     if (p.D != 64 && p.D != 128) return false;
     if (p.nd != 0) return false;
-    if (p.scale == 0.f) return false;  // hidden scores are -inf; -inf * 0 is not representable in the fast path
+    if (p.scale == 0.f || p.Sk < 2) return false;  // hidden scores are -inf; -inf * 0 is not representable in the fast path
     if (p.has_mask && p.ms[2] != 0) return false;  // only masks broadcast over the query axis
     if (!tma_compatible(p.q, p.qs, p.B, p.Hq, p.Sq) || !tma_compatible(p.k, p.ks, p.B, p.Hkv, p.Sk) ||
         !tma_compatible(p.v, p.vs, p.B, p.Hkv, p.Sk))

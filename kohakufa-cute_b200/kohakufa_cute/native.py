@@ -134,6 +134,12 @@ def _plain(tensor):
     return tensor.resolve_conj().resolve_neg()
 
 
+def _rows_16_byte_addressable(t):
+    if t.stride(-1) != 1 or t.data_ptr() % 16:
+        return False
+    return all(size == 1 or (stride > 0 and stride % 8 == 0) for size, stride in zip(t.shape[:-1], t.stride()[:-1]))
+
+
 def _blocks_shape(q, k, mask):
     return (
         1 if mask.stride(0) == 0 else q.shape[0],
@@ -164,6 +170,10 @@ def backward(q, k, v, mask, maximum, logsum, dout, blocks, out, scale, causal):
     """(dq, dk, dv) - mirrors the reference extension's ``backward`` (native.cpp:1038)."""
     lib = library()
     q, k, v, dout, out = _plain(q), _plain(k), _plain(v), _plain(dout), _plain(out)
+    if not _rows_16_byte_addressable(dout):
+        # expanded (stride-0), channel-strided or misaligned output gradients: the tensor-memory
+        # kernels address rows through TMA, so give them a dense copy
+        dout = dout.contiguous()
     with torch.cuda.device(q.device):
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         rq, rk = describe(q), describe(k)
