@@ -96,7 +96,7 @@ KFA_API int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_ten
  * Key centering: centered = round(f32(k) - mean over the sequence axis of f32(k)) per
  * (batch, head, channel).  Replaces the PyTorch expression at api.py:100-103.  The same
  * entry point computes the gradient projection (apply it to the centred-key gradient).
- * `workspace` holds B*H*D floats.
+ * `workspace` holds kfa_center_keys_workspace_bytes() bytes (partial column sums and the means).
  */
 KFA_API size_t kfa_center_keys_workspace_bytes(const kfa_tensor* k);
 KFA_API int kfa_center_keys(const kfa_tensor* k, kfa_tensor* centered, void* workspace, size_t workspace_bytes,

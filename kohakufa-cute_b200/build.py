@@ -22,6 +22,10 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-Wno-deprecated-gpu-targets"]
 
 
+if os.environ.get("KFA_TRACE"):  # tuning aid: cycle stamps from the CTA with this index
+    NVCC_FLAGS = NVCC_FLAGS + ["-DKFA_TRACE=" + os.environ["KFA_TRACE"]]
+
+
 def _nvcc():
     return os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc" if os.path.exists("/usr/local/cuda/bin/nvcc") else "nvcc")
 

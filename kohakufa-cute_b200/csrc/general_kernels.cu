@@ -449,39 +449,68 @@ __global__ void __launch_bounds__(128) pack_mask(AttnParams p, int nb, int nh, i
 }
 
 // --------------------------------------------------------------- centre keys
-// mean[b,h,d] over the sequence axis in FP32, then out = round(f32(k) - mean).
+// mean[b,h,d] over the sequence axis in FP32 (fixed summation order: rows strided by 8 inside a
+// block, then the sequence splits in ascending order), then out = round(f32(k) - mean).
+constexpr int kMeanSplits = 32;
+bool vector_ok(const void* ptr, const int64_t* s, int D);
+
 template <typename T>
-__global__ void __launch_bounds__(256) column_mean(const T* k, float* mean, int H, int S, int D, int64_t s0, int64_t s1,
-                                                   int64_t s2, int64_t s3) {
+__global__ void __launch_bounds__(256) column_partial(const T* k, float* partial, int H, int S, int D, int splits,
+                                                      int64_t s0, int64_t s1, int64_t s2, int64_t s3) {
     __shared__ float part[8][33];
-    const int bh = blockIdx.y, b = bh / H, h = bh % H;
+    const int bh = blockIdx.y, b = bh / H, h = bh % H, split = blockIdx.z;
     const int d = blockIdx.x * 32 + (threadIdx.x & 31);
     const int lane_s = threadIdx.x >> 5;
+    const int rows_per = (S + splits - 1) / splits;
+    const int r0 = split * rows_per, r1 = min(S, r0 + rows_per);
     const T* base = k + (int64_t)b * s0 + (int64_t)h * s1;
     float sum = 0.f;
     if (d < D)
-        for (int s = lane_s; s < S; s += 8) sum += to_float<T>(base[(int64_t)s * s2 + (int64_t)d * s3]);
+        for (int s = r0 + lane_s; s < r1; s += 8) sum += to_float<T>(base[(int64_t)s * s2 + (int64_t)d * s3]);
     part[lane_s][threadIdx.x & 31] = sum;
     __syncthreads();
     if (lane_s == 0 && d < D) {
         float total = 0.f;
         for (int i = 0; i < 8; ++i) total += part[i][threadIdx.x];
+        partial[((int64_t)bh * splits + split) * D + d] = total;
+    }
+}
+__global__ void __launch_bounds__(128) finish_mean(const float* partial, float* mean, int S, int D, int splits) {
+    const int bh = blockIdx.x;
+    for (int d = threadIdx.x; d < D; d += 128) {
+        float total = 0.f;
+        for (int i = 0; i < splits; ++i) total += partial[((int64_t)bh * splits + i) * D + d];
         mean[(int64_t)bh * D + d] = total / (float)S;
     }
 }
-template <typename T>
+// One thread per 8 consecutive channels (VEC) or per element.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) subtract_mean(const T* k, const float* mean, T* out, int H, int S, int D,
                                                      int64_t s0, int64_t s1, int64_t s2, int64_t s3, int64_t o0,
                                                      int64_t o1, int64_t o2, int64_t o3) {
     const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    const int64_t per = (int64_t)S * D;
-    const int bh = blockIdx.y;
-    if (idx >= per) return;
-    const int b = bh / H, h = bh % H;
-    const int s = (int)(idx / D), d = (int)(idx % D);
-    const float x = to_float<T>(k[(int64_t)b * s0 + (int64_t)h * s1 + (int64_t)s * s2 + (int64_t)d * s3]);
-    out[(int64_t)b * o0 + (int64_t)h * o1 + (int64_t)s * o2 + (int64_t)d * o3] =
-        from_float<T>(x - mean[(int64_t)bh * D + d]);
+    const int bh = blockIdx.y, b = bh / H, h = bh % H;
+    if (VEC) {
+        const int per_row = D / 8;
+        if (idx >= (int64_t)S * per_row) return;
+        const int s = (int)(idx / per_row), d = (int)(idx % per_row) * 8;
+        const uint4 raw = *reinterpret_cast<const uint4*>(k + (int64_t)b * s0 + (int64_t)h * s1 + (int64_t)s * s2 + d);
+        const float4 m0 = *reinterpret_cast<const float4*>(mean + (int64_t)bh * D + d);
+        const float4 m1 = *reinterpret_cast<const float4*>(mean + (int64_t)bh * D + d + 4);
+        const float mv[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        const T* e = reinterpret_cast<const T*>(&raw);
+        uint4 res;
+        T* r = reinterpret_cast<T*>(&res);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r[i] = from_float<T>(to_float<T>(e[i]) - mv[i]);
+        *reinterpret_cast<uint4*>(out + (int64_t)b * o0 + (int64_t)h * o1 + (int64_t)s * o2 + d) = res;
+    } else {
+        if (idx >= (int64_t)S * D) return;
+        const int s = (int)(idx / D), d = (int)(idx % D);
+        const float x = to_float<T>(k[(int64_t)b * s0 + (int64_t)h * s1 + (int64_t)s * s2 + (int64_t)d * s3]);
+        out[(int64_t)b * o0 + (int64_t)h * o1 + (int64_t)s * o2 + (int64_t)d * o3] =
+            from_float<T>(x - mean[(int64_t)bh * D + d]);
+    }
 }
 
 // -------------------------------------------------------------- ring merge
@@ -591,17 +620,27 @@ cudaError_t launch_general_backward(const AttnParams& p, bool bf16, int which, c
     return vec ? launch_backward_t<__half, true>(p, which, st) : launch_backward_t<__half, false>(p, which, st);
 }
 
-cudaError_t launch_center_keys(const void* k, void* out, float* mean, bool bf16, int B, int H, int S, int D,
+// workspace: kMeanSplits * B*H*D partial sums followed by B*H*D means
+cudaError_t launch_center_keys(const void* k, void* out, float* workspace, bool bf16, int B, int H, int S, int D,
                                const int64_t* ks, const int64_t* os, cudaStream_t st) {
-    dim3 g1((D + 31) / 32, B * H), g2((unsigned)blocks_for((int64_t)S * D, 256), B * H);
+    const int splits = max(1, min(kMeanSplits, S / 128));
+    float* partial = workspace;
+    float* mean = workspace + (int64_t)kMeanSplits * B * H * D;
+    const bool vec = vector_ok(k, ks, D) && vector_ok(out, os, D);
+    const int64_t items = vec ? (int64_t)S * (D / 8) : (int64_t)S * D;
+    dim3 g1((D + 31) / 32, B * H, splits), g3((unsigned)blocks_for(items, 256), B * H);
     if (bf16) {
-        column_mean<__nv_bfloat16><<<g1, 256, 0, st>>>((const __nv_bfloat16*)k, mean, H, S, D, ks[0], ks[1], ks[2], ks[3]);
-        subtract_mean<__nv_bfloat16><<<g2, 256, 0, st>>>((const __nv_bfloat16*)k, mean, (__nv_bfloat16*)out, H, S, D, ks[0],
-                                                         ks[1], ks[2], ks[3], os[0], os[1], os[2], os[3]);
+        using T = __nv_bfloat16;
+        column_partial<T><<<g1, 256, 0, st>>>((const T*)k, partial, H, S, D, splits, ks[0], ks[1], ks[2], ks[3]);
+        finish_mean<<<B * H, 128, 0, st>>>(partial, mean, S, D, splits);
+        if (vec) subtract_mean<T, true><<<g3, 256, 0, st>>>((const T*)k, mean, (T*)out, H, S, D, ks[0], ks[1], ks[2], ks[3], os[0], os[1], os[2], os[3]);
+        else subtract_mean<T, false><<<g3, 256, 0, st>>>((const T*)k, mean, (T*)out, H, S, D, ks[0], ks[1], ks[2], ks[3], os[0], os[1], os[2], os[3]);
     } else {
-        column_mean<__half><<<g1, 256, 0, st>>>((const __half*)k, mean, H, S, D, ks[0], ks[1], ks[2], ks[3]);
-        subtract_mean<__half><<<g2, 256, 0, st>>>((const __half*)k, mean, (__half*)out, H, S, D, ks[0], ks[1], ks[2],
-                                                  ks[3], os[0], os[1], os[2], os[3]);
+        using T = __half;
+        column_partial<T><<<g1, 256, 0, st>>>((const T*)k, partial, H, S, D, splits, ks[0], ks[1], ks[2], ks[3]);
+        finish_mean<<<B * H, 128, 0, st>>>(partial, mean, S, D, splits);
+        if (vec) subtract_mean<T, true><<<g3, 256, 0, st>>>((const T*)k, mean, (T*)out, H, S, D, ks[0], ks[1], ks[2], ks[3], os[0], os[1], os[2], os[3]);
+        else subtract_mean<T, false><<<g3, 256, 0, st>>>((const T*)k, mean, (T*)out, H, S, D, ks[0], ks[1], ks[2], ks[3], os[0], os[1], os[2], os[3]);
     }
     return cudaGetLastError();
 }

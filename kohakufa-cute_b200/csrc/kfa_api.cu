@@ -400,7 +400,8 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
 
 size_t kfa_center_keys_workspace_bytes(const kfa_tensor* k) {
     if (!k || k->ndim != 4) return 0;
-    return ((size_t)k->sizes[0] * k->sizes[1] * k->sizes[3] * sizeof(float) + 255) / 256 * 256;
+    // 32 sequence splits of partial column sums plus the means
+    return ((size_t)k->sizes[0] * k->sizes[1] * k->sizes[3] * sizeof(float) * 33 + 255) / 256 * 256;
 }
 
 int kfa_center_keys(const kfa_tensor* k, kfa_tensor* centered, void* workspace, size_t workspace_bytes, void* stream) {
@@ -419,7 +420,7 @@ int kfa_center_keys(const kfa_tensor* k, kfa_tensor* centered, void* workspace, 
                                        k->strides, centered->strides, st);
     });
     if (ce != cudaSuccess) return cuda_fail(ce, "center_keys launch");
-    g_launches += 1;  // two kernels per call
+    g_launches += 2;  // three kernels per call
     return 0;
 }
 

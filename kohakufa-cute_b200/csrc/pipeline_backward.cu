@@ -37,15 +37,15 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward(const __grid_co
         mbar_init(&sh.owner_full, 1);
         for (int s = 0; s < C::kPairs; ++s) {
             mbar_init(&sh.pair_full[s], 1);
-            mbar_init(&sh.pair_empty[s], 1);
+            mbar_init(&sh.pair_empty[s], 2);  // both MMA issuers release a slot
         }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&sh.sdp_ready[s], 1);
-            mbar_init(&sh.done[s], 128);
+            mbar_init(&sh.sdp_ready[s], 2);   // S from issuer 0, dP from issuer 1
+            mbar_init(&sh.done[s], 256);
             mbar_init(&sh.stats_full[s], 1);
             mbar_init(&sh.stats_empty[s], 256);
         }
-        mbar_init(&sh.final_done, 1);
+        mbar_init(&sh.final_done, 2);
         mbar_fence_init();
     }
     if (warp == 8) {
@@ -58,16 +58,16 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward(const __grid_co
     const uint32_t tmem = sh.tmem_base;
 
     if (warp >= 8) {
-        reg_dealloc<56>();
-        if (warp == 8) {
-            if (lane == 0) mma_role<D, BF16, KV>(p, w, sh, tmem, s_owner, s_ring);
-        } else if (warp == 9) {
-            if (lane == 0) loader_role<D, KV>(maps, p, w, sh, s_owner, s_ring);
+        reg_dealloc<96>();
+        if (warp <= 9) {
+            if (lane == 0) mma_role<D, BF16, KV>(p, w, sh, tmem, s_owner, s_ring, warp - 8);
         } else if (warp == 10) {
+            if (lane == 0) loader_role<D, KV>(maps, p, w, sh, s_owner, s_ring);
+        } else {
             if (KV) stats_role<KV>(p, w, sh, s_stats, lane);
         }
     } else {
-        reg_alloc<224>();
+        reg_alloc<200>();
         consumer_role<D, BF16, KV>(p, w, sh, tmem, s_stats, warp >> 2, warp, lane);
     }
     tc_fence_before();
@@ -166,6 +166,17 @@ cudaError_t launch_pipeline_delta(const AttnParams& p, bool bf16, cudaStream_t s
     }
     return cudaGetLastError();
 }
+
+#ifdef KFA_TRACE
+extern "C" __attribute__((visibility("default"))) int kfa_debug_trace(long long* out, int* counts) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_kfa_trace, sizeof(long long) * 4 * 1024);
+    cudaMemcpyFromSymbol(counts, g_kfa_trace_n, sizeof(int) * 4);
+    int zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_kfa_trace_n, zero, sizeof(zero));
+    return 0;
+}
+#endif
 
 int pipeline_configured_variants() { return pipeline_forward_variants() + __builtin_popcount(g_configured.load()); }
 void pipeline_forget_variants() {

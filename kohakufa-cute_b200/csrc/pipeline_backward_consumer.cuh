@@ -1,7 +1,7 @@
 // Consumer warpgroups of the backward pipeline: scores -> P -> dS, and the gradient epilogue.
 //
-// A consumer thread owns one owner row (tensor-memory lane) and the 64 columns of its
-// warpgroup's sub-tile.  Per element, in FP32:
+// A consumer thread owns one owner row (tensor-memory lane) and 32 of the 64 columns of every
+// sub-tile (warpgroup 0 the first 32, warpgroup 1 the rest).  Per element, in FP32:
 //   P      = ex2((s' - m) * |scale| * log2e - logsum)      s' arrives already sign-adjusted
 //   P_low  = round(P)                                       one rounding to the input type
 //   dS_low = round(P_low * (dP - delta))
@@ -22,7 +22,6 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
     const int owner_row = w.owner0 + r;
     const int owner_len = KV ? p.Sk : p.Sq;
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    const uint32_t s_addr = lane_base + wg * 128, dp_addr = s_addr + 64;
     const float c2 = fabsf(p.scale) * kLog2e;
     const uint64_t c2_pair = f2_pack(c2, c2);
 
@@ -40,103 +39,87 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
         if (row_m == -INFINITY) row_m = INFINITY;  // nothing visible: every P is zero
     }
 
+    // Both warpgroups work on every sub-tile: this one takes columns [wg*32, wg*32+32) of the 64.
+    constexpr int kCols = kSub / 2;
     int g, i;
     w.begin(p, g, i);
     int unit = 0;
     bool ok = true;
     while (w.valid(g) && ok) {
         if (KV) ok = mbar_wait(&sh.stats_full[unit & 1], (unit >> 1) & 1, abort_word, 140);
-        if (ok) ok = mbar_wait(&sh.sdp_ready[wg], unit & 1, abort_word, 141 + wg);
-        if (!ok) break;
-        tc_fence_after();
-        uint32_t s[kSub], dp[kSub];
-        {
-            uint32_t a[32], b2[32];
-            tmem_ld32(s_addr, a);
-            tmem_ld32(s_addr + 32, b2);
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                s[c] = a[c];
-                s[32 + c] = b2[c];
-            }
-            tmem_ld32(dp_addr, a);
-            tmem_ld32(dp_addr + 32, b2);
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                dp[c] = a[c];
-                dp[32 + c] = b2[c];
-            }
-        }
-        tmem_wait_ld();
+        const int state = KV ? 2 : key_tile_state(p, w.b, w.head, i);
+        for (int sub = 0; sub < 2 && ok; ++sub) {
+            KFA_TRACE_POINT(1 + wg, 1);
+            ok = mbar_wait(&sh.sdp_ready[sub], unit & 1, abort_word, 141 + sub);
+            if (!ok) break;
+            KFA_TRACE_POINT(1 + wg, 2);
+            tc_fence_after();
+            const uint32_t s_addr = lane_base + sub * 128 + wg * kCols, dp_addr = s_addr + 64;
+            uint32_t s[kCols], dp[kCols];
+            tmem_ld32(s_addr, s);
+            tmem_ld32(dp_addr, dp);
+            tmem_wait_ld();
+            KFA_TRACE_POINT(1 + wg, 3);
 
-        // visibility of the 64 columns of this sub-tile: columns [lo, hi) of this row are visible
-        const int col0 = i * kTile + wg * kSub;  // first streamed row (key or query) of the sub-tile
-        int lo = 0, hi = kSub;
-        int state = 2;
-        if (KV) {
-            if (p.causal) lo = owner_row - col0;  // query index must be >= key index
-            if (!row_ok) lo = kSub;
-        } else {
-            hi = p.Sk - col0;
-            if (p.causal) hi = min(hi, owner_row - col0 + 1);
-            state = key_tile_state(p, w.b, w.head, i);
-        }
-        const bool clip = __any_sync(0xffffffffu, lo > 0 || hi < kSub);
-        const float* st = s_stats + (unit & 1) * 3 * kTile + wg * kSub;
-
-        uint32_t pw[kSub / 2], dw[kSub / 2];
-#pragma unroll
-        for (int c = 0; c < kSub; c += 2) {
-            uint64_t m2, ls2, dl2;
+            // columns [lo, hi) of this thread's 32 are visible
+            const int col0 = i * kTile + sub * kSub + wg * kCols;  // first streamed row (key or query)
+            int lo = 0, hi = kCols;
             if (KV) {
-                const float2 mm = *reinterpret_cast<const float2*>(st + c);
-                const float2 ll = *reinterpret_cast<const float2*>(st + kTile + c);
-                const float2 dd = *reinterpret_cast<const float2*>(st + 2 * kTile + c);
-                m2 = f2_pack(mm.x, mm.y);
-                ls2 = f2_pack(ll.x, ll.y);
-                dl2 = f2_pack(dd.x, dd.y);
+                if (p.causal) lo = owner_row - col0;  // query index must be >= key index
+                if (!row_ok) lo = kCols;
             } else {
-                m2 = f2_pack(row_m, row_m);
-                ls2 = f2_pack(row_ls, row_ls);
-                dl2 = f2_pack(row_dl, row_dl);
+                hi = p.Sk - col0;
+                if (p.causal) hi = min(hi, owner_row - col0 + 1);
             }
-            const uint64_t s2 = f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1]));
-            float ea, eb;
-            f2_unpack(f2_sub(f2_mul(f2_sub(s2, m2), c2_pair), ls2), ea, eb);
-            float pa = ex2(ea), pb = ex2(eb);
-            if (clip) {
-                pa = (c >= lo && c < hi) ? pa : 0.f;
-                pb = (c + 1 >= lo && c + 1 < hi) ? pb : 0.f;
+            const bool clip = __any_sync(0xffffffffu, lo > 0 || hi < kCols);
+            const float* st = s_stats + (unit & 1) * 3 * kTile + sub * kSub + wg * kCols;
+
+            uint32_t pw[kCols / 2], dw[kCols / 2];
+#pragma unroll
+            for (int c = 0; c < kCols; c += 2) {
+                uint64_t m2, ls2, dl2;
+                if (KV) {
+                    const float2 mm = *reinterpret_cast<const float2*>(st + c);
+                    const float2 ll = *reinterpret_cast<const float2*>(st + kTile + c);
+                    const float2 dd = *reinterpret_cast<const float2*>(st + 2 * kTile + c);
+                    m2 = f2_pack(mm.x, mm.y);
+                    ls2 = f2_pack(ll.x, ll.y);
+                    dl2 = f2_pack(dd.x, dd.y);
+                } else {
+                    m2 = f2_pack(row_m, row_m);
+                    ls2 = f2_pack(row_ls, row_ls);
+                    dl2 = f2_pack(row_dl, row_dl);
+                }
+                const uint64_t s2 = f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+                float ea, eb;
+                f2_unpack(f2_sub(f2_mul(f2_sub(s2, m2), c2_pair), ls2), ea, eb);
+                float pa = ex2(ea), pb = ex2(eb);
+                if (clip) {
+                    pa = (c >= lo && c < hi) ? pa : 0.f;
+                    pb = (c + 1 >= lo && c + 1 < hi) ? pb : 0.f;
+                }
+                if (!KV && state == 1) {
+                    pa = kmask[(int64_t)min(col0 + c, p.Sk - 1) * p.ms[3]] != 0 ? pa : 0.f;
+                    pb = kmask[(int64_t)min(col0 + c + 1, p.Sk - 1) * p.ms[3]] != 0 ? pb : 0.f;
+                }
+                const uint32_t packed = pack2<BF16>(pa, pb);
+                pw[c / 2] = packed;
+                const float2 pl = unpack2<BF16>(packed);
+                const uint64_t res = f2_sub(f2_pack(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), dl2);
+                float da, db;
+                f2_unpack(f2_mul(f2_pack(pl.x, pl.y), res), da, db);
+                dw[c / 2] = pack2<BF16>(da, db);
             }
-            if (!KV && state == 1) {
-                pa = kmask[(int64_t)min(col0 + c, p.Sk - 1) * p.ms[3]] != 0 ? pa : 0.f;
-                pb = kmask[(int64_t)min(col0 + c + 1, p.Sk - 1) * p.ms[3]] != 0 ? pb : 0.f;
-            }
-            const uint32_t packed = pack2<BF16>(pa, pb);
-            pw[c / 2] = packed;
-            const float2 pl = unpack2<BF16>(packed);
-            const uint64_t res = f2_sub(f2_pack(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), dl2);
-            float da, db;
-            f2_unpack(f2_mul(f2_pack(pl.x, pl.y), res), da, db);
-            dw[c / 2] = pack2<BF16>(da, db);
+            // P_low over the head of this thread's S columns (key owners only), dS_low over its dP columns
+            KFA_TRACE_POINT(1 + wg, 4);
+            if (KV) tmem_st16(s_addr, pw);
+            tmem_st16(dp_addr, dw);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sh.done[sub]);
+            KFA_TRACE_POINT(1 + wg, 5);
         }
-        // P_low over the head of the S buffer (only key owners use it), dS_low over the head of dP
-        if (KV) {
-            uint32_t (&half0)[16] = *reinterpret_cast<uint32_t(*)[16]>(&pw[0]);
-            uint32_t (&half1)[16] = *reinterpret_cast<uint32_t(*)[16]>(&pw[16]);
-            tmem_st16(s_addr, half0);
-            tmem_st16(s_addr + 16, half1);
-        }
-        {
-            uint32_t (&half0)[16] = *reinterpret_cast<uint32_t(*)[16]>(&dw[0]);
-            uint32_t (&half1)[16] = *reinterpret_cast<uint32_t(*)[16]>(&dw[16]);
-            tmem_st16(dp_addr, half0);
-            tmem_st16(dp_addr + 16, half1);
-        }
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&sh.done[wg]);
-        if (KV) mbar_arrive(&sh.stats_empty[unit & 1]);
+        if (KV && ok) mbar_arrive(&sh.stats_empty[unit & 1]);
         w.next(p, g, i);
         ++unit;
     }

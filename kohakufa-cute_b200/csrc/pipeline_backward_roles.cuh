@@ -8,9 +8,9 @@
 //   KV = true   a CTA owns 128 key rows of one (batch, K/V head) and streams the query tiles of
 //               every query head in the group; it produces dK = (sum dS_low^T Q) * scale and
 //               dV = sum P_low^T dO.  One owner per output row, so no atomics are needed.
-// Each streamed 128-row tile is processed as two 64-wide sub-tiles that ping-pong between two
-// consumer warpgroups: while one warpgroup turns scores into P and dS, the tensor core works on
-// the other sub-tile.  Per sub-tile the tensor core runs
+// Each streamed 128-row tile is processed as two 64-wide sub-tiles in two tensor-memory buffers:
+// while the two consumer warpgroups turn one sub-tile's scores into P and dS (32 columns each),
+// the tensor core works on the other sub-tile.  Per sub-tile the tensor core runs
 //   S  = A1 x B1^T   (A1 = owner operand 1: Q or K;  B1 = streamed operand 1: K or Q)
 //   dP = A2 x B2^T   (A2 = owner operand 2: dO or V; B2 = streamed operand 2: V or dO)
 //   grad1 += dS_low x B1      (dQ, or dK)          A operand read from tensor memory
@@ -28,7 +28,7 @@ namespace bwd {
 
 constexpr int kTile = 128;     // owner rows, and rows of a streamed tile
 constexpr int kSub = 64;       // columns of one sub-tile
-constexpr int kThreads = 384;  // consumer WG 0, consumer WG 1, (MMA, loader, statistics, idle)
+constexpr int kThreads = 384;  // consumer WG 0, consumer WG 1, (MMA issuer 0, MMA issuer 1, loader, statistics)
 constexpr int kMaxPairs = 4;
 
 template <int D>
@@ -162,49 +162,56 @@ __device__ __forceinline__ void loader_role(const Maps& maps, const AttnParams& 
     }
 }
 
+// Two threads issue the tensor-core work, each its own in-order chain per sub-tile buffer b:
+//   chain 0:  grad2 += P_low x B2 (key owners) ... then S_b of the sub-tile after next
+//   chain 1:  grad1 += dS_low x B1            ... then dP_b of the sub-tile after next
+// A tcgen05.mma occupies its issuing thread for about a hundred cycles, so two issuers keep the
+// tensor core much busier than one.  The split follows the buffers: everything that reads or
+// overwrites S_b (and the P_low packed into it) is in chain 0, everything that touches dP_b
+// (and dS_low) in chain 1, so no ordering between the two threads is needed.
 template <int D, bool BF16, bool KV>
 __device__ __forceinline__ void mma_role(const AttnParams& p, const Work<KV>& w, Shared& sh, uint32_t tmem,
-                                         uint8_t* s_owner, uint8_t* s_ring) {
+                                         uint8_t* s_owner, uint8_t* s_ring, int chain) {
     using C = Cfg<D>;
     volatile int* abort_word = &sh.abort_word;
     int g, i;
     w.begin(p, g, i);
     if (!w.valid(g)) return;
     // A negative scale takes maxima over -S: the forward saved statistics of -S, so negate operand A.
-    const uint32_t idesc_s = umma_idesc(kTile, kSub, BF16 ? 1 : 0, false, false) | (p.scale < 0.f ? kUmmaNegateA : 0u);
-    constexpr uint32_t idesc_p = umma_idesc(kTile, kSub, BF16 ? 1 : 0, false, false);
+    const uint32_t idesc_s = umma_idesc(kTile, kSub, BF16 ? 1 : 0, false, false) |
+                             (chain == 0 && p.scale < 0.f ? kUmmaNegateA : 0u);
     constexpr uint32_t idesc_g = umma_idesc(kTile, D, BF16 ? 1 : 0, false, true);
-    const uint32_t own1 = smem_u32(s_owner), own2 = own1 + C::kTileBytes, ring = smem_u32(s_ring);
+    // chain 0 works with owner/streamed operand 1 for scores and streamed operand 2 for its gradient;
+    // chain 1 the other way round.
+    const uint32_t own = smem_u32(s_owner) + chain * C::kTileBytes, ring = smem_u32(s_ring);
+    const uint32_t score_src = chain * C::kTileBytes;        // streamed operand feeding S (0) / dP (1)
+    const uint32_t grad_src = (1 - chain) * C::kTileBytes;   // streamed operand feeding grad2 (0) / grad1 (1)
+    const uint32_t grad_col = tmem + (chain == 0 ? 256 : 384);
+    const bool has_grad = KV || chain == 1;
+    // Descriptors are built once; per instruction only the start-address field advances.
+    const uint64_t own_desc = umma_desc_sw128(own, 16, 1024);
+    const uint64_t ring_k_desc = umma_desc_sw128(ring, 16, 1024);            // K-major view (score products)
+    const uint64_t ring_mn_desc = umma_desc_sw128(ring, kTile * 128, 1024);  // MN-major view (gradient products)
 
-    // S_b and dP_b of sub-tile `sub` of the pair in `slot`
     auto issue_scores = [&](int slot, int sub) {
-        const uint32_t st1 = ring + slot * 2 * C::kTileBytes, st2 = st1 + C::kTileBytes;
-        const uint32_t s_col = tmem + sub * 128, dp_col = s_col + 64;
+        const uint32_t st = slot * 2 * C::kTileBytes + score_src + sub * 8192;
+        const uint32_t col = tmem + sub * 128 + chain * 64;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
             const uint32_t off = (kk / 4) * (kTile * 128) + (kk % 4) * 32;
-            umma_ss(s_col, umma_desc_sw128(own1 + off, 16, 1024), umma_desc_sw128(st1 + sub * 8192 + off, 16, 1024),
-                    idesc_s, kk > 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t off = (kk / 4) * (kTile * 128) + (kk % 4) * 32;
-            umma_ss(dp_col, umma_desc_sw128(own2 + off, 16, 1024), umma_desc_sw128(st2 + sub * 8192 + off, 16, 1024),
-                    idesc_p, kk > 0);
+            umma_ss(col, umma_desc_advance(own_desc, off), umma_desc_advance(ring_k_desc, st + off), idesc_s, kk > 0);
         }
         umma_commit(&sh.sdp_ready[sub]);
     };
-    // gradient accumulation of sub-tile `sub`: A operands are the packed P / dS in tensor memory
     auto issue_grads = [&](int slot, int sub, bool accumulate) {
-        const uint32_t st1 = ring + slot * 2 * C::kTileBytes, st2 = st1 + C::kTileBytes;
-        const uint32_t p_col = tmem + sub * 128, ds_col = p_col + 64;
+        const uint32_t st = slot * 2 * C::kTileBytes + grad_src;
+        const uint32_t a_col = tmem + sub * 128 + chain * 64;
 #pragma unroll
         for (int kk = 0; kk < kSub / 16; ++kk) {
             const uint32_t rows = (sub * 4 + kk) * 2048;  // 16 streamed rows per step, 128 bytes each
-            if (KV)
-                umma_ts(tmem + 256, p_col + kk * 8, umma_desc_sw128(st2 + rows, kTile * 128, 1024), idesc_g,
-                        accumulate || kk > 0);
-            umma_ts(tmem + 384, ds_col + kk * 8, umma_desc_sw128(st1 + rows, kTile * 128, 1024), idesc_g,
+            // each consumer warpgroup packs its 32 columns into the first 16 columns of its own range
+            const uint32_t a_off = (kk >> 1) * 32 + (kk & 1) * 8;
+            umma_ts(grad_col, a_col + a_off, umma_desc_advance(ring_mn_desc, st + rows), idesc_g,
                     accumulate || kk > 0);
         }
     };
@@ -222,10 +229,13 @@ __device__ __forceinline__ void mma_role(const AttnParams& p, const Work<KV>& w,
         const bool more = w.valid(gn);
         const int slot = unit % C::kPairs, nslot = (unit + 1) % C::kPairs;
         for (int sub = 0; sub < 2 && ok; ++sub) {
+            KFA_TRACE_POINT(0, 1);
             ok = mbar_wait(&sh.done[sub], unit & 1, abort_word, 122 + sub);
             if (!ok) break;
+            KFA_TRACE_POINT(0, 2);
             tc_fence_after();
-            issue_grads(slot, sub, unit > 0 || sub > 0);
+            if (has_grad) issue_grads(slot, sub, unit > 0 || sub > 0);
+            KFA_TRACE_POINT(0, 3);
             if (sub == 1) umma_commit(&sh.pair_empty[slot]);
             if (more) {
                 if (sub == 0) {
@@ -234,6 +244,7 @@ __device__ __forceinline__ void mma_role(const AttnParams& p, const Work<KV>& w,
                     tc_fence_after();
                 }
                 issue_scores(nslot, sub);
+                KFA_TRACE_POINT(0, 4);
             }
         }
         g = gn;

@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
     volatile int* abort_word = &sh.abort_word;
 
     if (warp >= 8) {
-      reg_dealloc<40>();
+      reg_dealloc<88>();
       if (warp == 9) {
         // ------------------------------------------------------------ loader
         if (lane == 0) {
@@ -166,21 +166,24 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                 umma_idesc(kTileQ, kTileK, BF16 ? 1 : 0, false, false) | (p.scale < 0.f ? kUmmaNegateA : 0u);
             constexpr uint32_t idesc_o = umma_idesc(kTileQ, D, BF16 ? 1 : 0, false, true);
             const uint32_t q_addr = smem_u32(sQ), kv_addr = smem_u32(sKV);
+            // Descriptors are built once; per instruction only the start-address field advances.
+            const uint64_t q_desc = umma_desc_sw128(q_addr, 16, 1024), k_desc = umma_desc_sw128(kv_addr, 16, 1024);
+            const uint64_t v_desc = umma_desc_sw128(kv_addr, kTileK * 128, 1024);
             auto issue_s = [&](int t, int slot) {
-                const uint32_t a0 = q_addr + t * Cfg::kTileBytes, b0 = kv_addr + slot * Cfg::kTileBytes;
+                const uint32_t a0 = t * Cfg::kTileBytes, b0 = slot * Cfg::kTileBytes;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk / 4) * (kTileQ * 128) + (kk % 4) * 32;
-                    umma_ss(tmem + t * 128, umma_desc_sw128(a0 + off, 16, 1024), umma_desc_sw128(b0 + off, 16, 1024),
+                    umma_ss(tmem + t * 128, umma_desc_advance(q_desc, a0 + off), umma_desc_advance(k_desc, b0 + off),
                             idesc_s, kk > 0);
                 }
             };
             auto issue_o = [&](int t, int slot, bool accumulate) {
-                const uint32_t b0 = kv_addr + slot * Cfg::kTileBytes;
+                const uint32_t b0 = slot * Cfg::kTileBytes;
 #pragma unroll
                 for (int kk = 0; kk < kTileK / 16; ++kk)
-                    umma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8,
-                            umma_desc_sw128(b0 + kk * 2048, kTileK * 128, 1024), idesc_o, accumulate || kk > 0);
+                    umma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, umma_desc_advance(v_desc, b0 + kk * 2048),
+                            idesc_o, accumulate || kk > 0);
             };
             bool ok = mbar_wait(&sh.q_full, 0, abort_word, 20);
             int slot_use = 0, iter[2] = {0, 0};
@@ -240,7 +243,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
         }
       }
     } else {
-        reg_alloc<232>();
+        reg_alloc<208>();
         // ---------------------------------------------------------- softmax
         const int t = warp >> 2;
         const int row_in_tile = (warp & 3) * 32 + lane;

@@ -13,6 +13,26 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+// Optional cycle-stamp tracing of one CTA for tuning (compiled in only with -DKFA_TRACE).
+#ifdef KFA_TRACE
+static __device__ long long g_kfa_trace[4][1024];
+static __device__ int g_kfa_trace_n[4];
+#define KFA_TRACE_POINT(stream, tag)                                              \
+    do {                                                                          \
+        if (blockIdx.x == KFA_TRACE && (threadIdx.x == 0 || threadIdx.x == 128 || threadIdx.x == 256)) {                 \
+            int n_ = g_kfa_trace_n[stream];                                       \
+            if (n_ < 1024) {                                                      \
+                g_kfa_trace[stream][n_] = (clock64() << 4) | (tag);               \
+                g_kfa_trace_n[stream] = n_ + 1;                                   \
+            }                                                                     \
+        }                                                                         \
+    } while (0)
+#else
+#define KFA_TRACE_POINT(stream, tag) \
+    do {                             \
+    } while (0)
+#endif
+
 namespace kfa {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -118,6 +138,11 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr, uint32_t lbo
     d |= 1ull << 46;  // descriptor version for sm_100
     d |= 2ull << 61;  // SWIZZLE_128B
     return d;
+}
+
+// Descriptor of the same tile shifted by `bytes` (a multiple of 16 that stays inside shared memory).
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) {
+    return desc + static_cast<uint64_t>(bytes >> 4);
 }
 
 // Instruction descriptor for kind::f16 with an FP32 accumulator.
