@@ -77,6 +77,14 @@ KFA_API int kfa_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tens
                 kfa_tensor* out, kfa_tensor* maximum, kfa_tensor* logsum, kfa_tensor* blocks, float scale,
                 int causal, void* stream);
 
+/*
+ * Classifies the 64x64 tiles of an expanded boolean mask (0 hidden, 1 mixed, 2 fully visible) into
+ * `blocks`, laid out as kfa_forward documents.  kfa_forward does this itself; the separate entry
+ * point serves callers that run kfa_backward against a (query shard, key block) pair for which no
+ * forward call produced a table.  Replaces the PackMask kernel launch (kernels.py:3170-3198).
+ */
+KFA_API int kfa_pack_mask(const kfa_tensor* mask, kfa_tensor* blocks, void* stream);
+
 /* Bytes of scratch kfa_backward needs for these shapes (native.cpp:341-354 sizes the
  * same buffers: delta and its base). */
 KFA_API size_t kfa_backward_workspace_bytes(const kfa_tensor* q, const kfa_tensor* k);

@@ -339,6 +339,30 @@ int kfa_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, c
     return 0;
 }
 
+int kfa_pack_mask(const kfa_tensor* mask, kfa_tensor* blocks, void* stream) {
+    if (!mask || !mask->data || mask->dtype != KFA_BOOL || mask->ndim != 4)
+        return fail(KFA_INVALID_ARGUMENT, "pack_mask requires a boolean mask expanded to [B,Hq,Sq,Sk]");
+    for (int i = 0; i < 4; ++i)
+        if (mask->sizes[i] <= 0 || mask->sizes[i] > INT32_MAX) return fail(KFA_INVALID_ARGUMENT, "pack_mask: bad extent");
+    kfa::AttnParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.B = (int)mask->sizes[0];
+    p.Hq = (int)mask->sizes[1];
+    p.Sq = (int)mask->sizes[2];
+    p.Sk = (int)mask->sizes[3];
+    p.mask = static_cast<const uint8_t*>(mask->data);
+    copy4(p.ms, mask->strides);
+    p.has_mask = 1;
+    if (int e = bind_blocks(p, blocks)) return e;
+    int64_t n[4];
+    block_extents(p, n);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t ce =
+        timed("pack_mask", st, [&] { return kfa::launch_pack_mask(p, (int)n[0], (int)n[1], (int)n[2], (int)n[3], st); });
+    if (ce != cudaSuccess) return cuda_fail(ce, "pack_mask launch");
+    return 0;
+}
+
 size_t kfa_backward_workspace_bytes(const kfa_tensor* q, const kfa_tensor* k) {
     (void)k;
     if (!q || q->ndim != 4) return 0;

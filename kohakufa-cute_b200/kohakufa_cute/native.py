@@ -47,6 +47,7 @@ SIGNATURES = {
     "kfa_last_error": (ctypes.c_char_p, []),
     "kfa_forward": (ctypes.c_int, [_TP, _TP, _TP, _TP, _TP, _TP, _TP, _TP, ctypes.c_float, ctypes.c_int,
                                    ctypes.c_void_p]),
+    "kfa_pack_mask": (ctypes.c_int, [_TP, _TP, ctypes.c_void_p]),
     "kfa_backward_workspace_bytes": (ctypes.c_size_t, [_TP, _TP]),
     "kfa_backward": (ctypes.c_int, [_TP] * 12 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float, ctypes.c_int,
                                                  ctypes.c_void_p]),
@@ -164,6 +165,16 @@ def forward(q, k, v, mask, scale, causal):
         records = [describe(t) for t in (q, k, v, mask, out, maximum, logsum, blocks if mask is not None else None)]
         _check(lib.kfa_forward(*[_ref(r) for r in records], float(scale), int(bool(causal)), _stream(q.device)))
     return out, maximum, logsum, blocks
+
+
+def pack_mask(q, k, mask):
+    """int32 tile table of an expanded [B,Hq,Sq,Sk] boolean mask (see ``kfa_pack_mask``)."""
+    lib = library()
+    with torch.cuda.device(q.device):
+        blocks = torch.empty(_blocks_shape(q, k, mask), device=q.device, dtype=torch.int32)
+        rm, rb = describe(mask), describe(blocks)
+        _check(lib.kfa_pack_mask(_ref(rm), _ref(rb), _stream(q.device)))
+    return blocks
 
 
 def backward(q, k, v, mask, maximum, logsum, dout, blocks, out, scale, causal):
