@@ -111,6 +111,20 @@ KFA_API int kfa_center_keys(const kfa_tensor* k, kfa_tensor* centered, void* wor
                     void* stream);
 
 /*
+ * Key centering for callers that must not allocate: same result as kfa_center_keys, but the
+ * scratch lives in a fixed array inside the library image instead of caller memory, and the
+ * call makes no allocation of any kind.  (This entry point has no counterpart in the reference
+ * project.)  Limits and rules:
+ *   - batch * heads * channels must not exceed kfa_center_keys_static_limit() (16384); larger
+ *     problems return KFA_TOO_LARGE and launch nothing;
+ *   - every GPU that loads the library holds the array (about 2.1 MB) until the process exits;
+ *   - all calls share the array: calls that overlap in time on one GPU race with each other;
+ *   - the first call on a device looks up the array's address; make it before any stream capture.
+ */
+KFA_API size_t kfa_center_keys_static_limit(void);
+KFA_API int kfa_center_keys_static(const kfa_tensor* k, kfa_tensor* centered, void* stream);
+
+/*
  * Neighbourhood (shifted-window) attention, head dim 64, equal Q/K/V shapes
  * [B,H,prod(spatial),64].  Replaces `neighborhood_forward` (native.cpp:1043-1054) and the
  * Python-side backward launch (neighborhood_kernels.py:408-411).  `nd` is 2 or 3.

@@ -222,6 +222,11 @@ int geometry(kfa::AttnParams& p, const int64_t* spatial, int nd, const int64_t* 
 
 }  // namespace
 
+namespace kfa {
+void note_failure(int code, const char* message) { fail(code, "%s", message); }
+void count_launches(int n) { g_launches += (uint64_t)n; }
+}  // namespace kfa
+
 extern "C" {
 
 int kfa_version(void) { return (0 << 16) | 1; }

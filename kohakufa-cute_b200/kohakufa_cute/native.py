@@ -53,6 +53,8 @@ SIGNATURES = {
                                                  ctypes.c_void_p]),
     "kfa_center_keys_workspace_bytes": (ctypes.c_size_t, [_TP]),
     "kfa_center_keys": (ctypes.c_int, [_TP, _TP, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "kfa_center_keys_static_limit": (ctypes.c_size_t, []),
+    "kfa_center_keys_static": (ctypes.c_int, [_TP, _TP, ctypes.c_void_p]),
     "kfa_neighborhood_forward": (ctypes.c_int, [_TP] * 6 + [_I64P, ctypes.c_int, _I64P, ctypes.c_float,
                                                             ctypes.c_void_p]),
     "kfa_neighborhood_backward_workspace_bytes": (ctypes.c_size_t, [_TP]),
@@ -210,6 +212,22 @@ def center_keys(k):
         ro = describe(out)
         _check(lib.kfa_center_keys(_ref(rk), _ref(ro), ctypes.c_void_p(workspace.data_ptr()), need,
                                    _stream(k.device)))
+    return out
+
+
+def center_keys_static(k, out=None):
+    """Key centring through the entry point that allocates nothing: the scratch is a fixed array
+    inside the library (see ``kfa_center_keys_static``).  ``out`` is the caller's output tensor;
+    when omitted one is created here, which is a convenience of this binding, not of the C call.
+    Raises ``RuntimeError`` when batch*heads*channels exceeds ``kfa_center_keys_static_limit()``.
+    """
+    lib = library()
+    k = _plain(k)
+    with torch.cuda.device(k.device):
+        if out is None:
+            out = torch.empty_like(k)
+        rk, ro = describe(k), describe(out)
+        _check(lib.kfa_center_keys_static(_ref(rk), _ref(ro), _stream(k.device)))
     return out
 
 
