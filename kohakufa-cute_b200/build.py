@@ -26,6 +26,10 @@ if os.environ.get("KFA_TRACE"):  # tuning aid: cycle stamps from the CTA with th
     NVCC_FLAGS = NVCC_FLAGS + ["-DKFA_TRACE=" + os.environ["KFA_TRACE"]]
 
 
+if os.environ.get("KFA_DEFINES"):  # tuning aid: extra -D switches, space separated
+    NVCC_FLAGS = NVCC_FLAGS + ["-D" + d for d in os.environ["KFA_DEFINES"].split()]
+
+
 def _nvcc():
     return os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc" if os.path.exists("/usr/local/cuda/bin/nvcc") else "nvcc")
 

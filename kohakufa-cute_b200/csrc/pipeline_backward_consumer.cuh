@@ -75,40 +75,54 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
             const float* st = s_stats + (unit & 1) * 3 * kTile + sub * kSub + wg * kCols;
 
             uint32_t pw[kCols / 2], dw[kCols / 2];
-#pragma unroll
-            for (int c = 0; c < kCols; c += 2) {
-                uint64_t m2, ls2, dl2;
+            const bool masked = clip || (!KV && state == 1);
+            // One pair of columns: probabilities, their rounding, and the rounded score gradient.
+            auto pair = [&](int c, bool apply_mask) {
+                float m0, m1, l0, l1, d0, d1;
                 if (KV) {
                     const float2 mm = *reinterpret_cast<const float2*>(st + c);
                     const float2 ll = *reinterpret_cast<const float2*>(st + kTile + c);
                     const float2 dd = *reinterpret_cast<const float2*>(st + 2 * kTile + c);
-                    m2 = f2_pack(mm.x, mm.y);
-                    ls2 = f2_pack(ll.x, ll.y);
-                    dl2 = f2_pack(dd.x, dd.y);
+                    m0 = mm.x, m1 = mm.y, l0 = ll.x, l1 = ll.y, d0 = dd.x, d1 = dd.y;
                 } else {
-                    m2 = f2_pack(row_m, row_m);
-                    ls2 = f2_pack(row_ls, row_ls);
-                    dl2 = f2_pack(row_dl, row_dl);
+                    m0 = m1 = row_m, l0 = l1 = row_ls, d0 = d1 = row_dl;
                 }
-                const uint64_t s2 = f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+#ifdef KFA_SCALAR_MATH
+                float pa = ex2((__uint_as_float(s[c]) - m0) * c2 - l0);
+                float pb = ex2((__uint_as_float(s[c + 1]) - m1) * c2 - l1);
+#else
                 float ea, eb;
-                f2_unpack(f2_sub(f2_mul(f2_sub(s2, m2), c2_pair), ls2), ea, eb);
+                f2_unpack(f2_sub(f2_mul(f2_sub(f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1])),
+                                               f2_pack(m0, m1)), c2_pair), f2_pack(l0, l1)), ea, eb);
                 float pa = ex2(ea), pb = ex2(eb);
-                if (clip) {
+#endif
+                if (apply_mask) {
                     pa = (c >= lo && c < hi) ? pa : 0.f;
                     pb = (c + 1 >= lo && c + 1 < hi) ? pb : 0.f;
-                }
-                if (!KV && state == 1) {
-                    pa = kmask[(int64_t)min(col0 + c, p.Sk - 1) * p.ms[3]] != 0 ? pa : 0.f;
-                    pb = kmask[(int64_t)min(col0 + c + 1, p.Sk - 1) * p.ms[3]] != 0 ? pb : 0.f;
+                    if (!KV && state == 1) {
+                        pa = kmask[(int64_t)min(col0 + c, p.Sk - 1) * p.ms[3]] != 0 ? pa : 0.f;
+                        pb = kmask[(int64_t)min(col0 + c + 1, p.Sk - 1) * p.ms[3]] != 0 ? pb : 0.f;
+                    }
                 }
                 const uint32_t packed = pack2<BF16>(pa, pb);
                 pw[c / 2] = packed;
                 const float2 pl = unpack2<BF16>(packed);
-                const uint64_t res = f2_sub(f2_pack(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), dl2);
+#ifdef KFA_SCALAR_MATH
+                const float da = pl.x * (__uint_as_float(dp[c]) - d0), db = pl.y * (__uint_as_float(dp[c + 1]) - d1);
+#else
                 float da, db;
-                f2_unpack(f2_mul(f2_pack(pl.x, pl.y), res), da, db);
+                f2_unpack(f2_mul(f2_pack(pl.x, pl.y),
+                                 f2_sub(f2_pack(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), f2_pack(d0, d1))),
+                          da, db);
+#endif
                 dw[c / 2] = pack2<BF16>(da, db);
+            };
+            if (masked) {
+#pragma unroll
+                for (int c = 0; c < kCols; c += 2) pair(c, true);
+            } else {
+#pragma unroll
+                for (int c = 0; c < kCols; c += 2) pair(c, false);
             }
             // P_low over the head of this thread's S columns (key owners only), dS_low over its dP columns
             KFA_TRACE_POINT(1 + wg, 4);

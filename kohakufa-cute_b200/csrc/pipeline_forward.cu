@@ -219,10 +219,13 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                 bool k_waited = false;
                 for (int t = 0; t < 2 && ok; ++t) {
                     if (j >= n_t[t]) continue;
+                    KFA_TRACE_POINT(0, 1);
                     ok = mbar_wait(&sh.p_ready[t], iter[t] & 1, abort_word, 23 + t);
                     if (!ok) break;
+                    KFA_TRACE_POINT(0, 2);
                     tc_fence_after();
                     issue_o(t, v_slot, iter[t] > 0);
+                    KFA_TRACE_POINT(0, 3);
                     if (jn < n_t[t]) {
                         if (!k_waited) {
                             ok = mbar_wait(&sh.kv_full[k_slot], k_par, abort_word, 25);
@@ -233,6 +236,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                         issue_s(t, k_slot);
                     }
                     umma_commit(&sh.s_ready[t]);
+                    KFA_TRACE_POINT(0, 4);
                     ++iter[t];
                 }
                 if (!ok) break;
@@ -259,8 +263,10 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
         for (int j = 0; j < n_t[t] && ok; ++j) {
             const int state = key_tile_state(p, b, h, j);
             if (state == 0) continue;
+            KFA_TRACE_POINT(1 + t, 1);
             ok = mbar_wait(&sh.s_ready[t], iter & 1, abort_word, 30 + t);
             if (!ok) break;
+            KFA_TRACE_POINT(1 + t, 2);
             tc_fence_after();
             // scores arrive already multiplied by sign(scale) (negated A operand for negative scales)
             float s[kTileK];
@@ -272,6 +278,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                 for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(r[i]);
             }
             tmem_wait_ld();
+            KFA_TRACE_POINT(1 + t, 3);
             const int key0 = j * kTileK;
             // leading columns of this tile that pass the sequence-end and causal bounds for this row
             int lim = p.Sk - key0;
@@ -313,6 +320,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                     tmem_st32(o_addr + c, r);
                 }
             }
+            KFA_TRACE_POINT(1 + t, 4);
             const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
             const uint64_t m_pair = f2_pack(m_safe, m_safe);
             uint64_t sum_a = f2_pack(0.f, 0.f), sum_b = sum_a;
@@ -345,6 +353,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&sh.p_ready[t]);
+            KFA_TRACE_POINT(1 + t, 5);
             ++iter;
         }
         // epilogue: wait for the last product, normalise, store
@@ -437,6 +446,17 @@ cudaError_t launch_pipeline_forward(const AttnParams& p, bool bf16, cudaStream_t
     if (p.D == 128) return bf16 ? launch_t<128, true>(p, st) : launch_t<128, false>(p, st);
     return bf16 ? launch_t<64, true>(p, st) : launch_t<64, false>(p, st);
 }
+
+#ifdef KFA_TRACE
+extern "C" __attribute__((visibility("default"))) int kfa_debug_trace_fwd(long long* out, int* counts) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_kfa_trace, sizeof(long long) * 4 * 1024);
+    cudaMemcpyFromSymbol(counts, g_kfa_trace_n, sizeof(int) * 4);
+    int zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_kfa_trace_n, zero, sizeof(zero));
+    return 0;
+}
+#endif
 
 int pipeline_forward_variants() { return __builtin_popcount(g_configured.load()); }
 void pipeline_forward_forget() { g_configured = 0; }
