@@ -41,14 +41,14 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward(const __grid_co
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&sh.sdp_ready[s], 2);   // S from issuer 0, dP from issuer 1
-            mbar_init(&sh.done[s], 256);
+            mbar_init(&sh.done[s], kConsumers);
             mbar_init(&sh.stats_full[s], 1);
-            mbar_init(&sh.stats_empty[s], 256);
+            mbar_init(&sh.stats_empty[s], kConsumers);
         }
         mbar_init(&sh.final_done, 2);
         mbar_fence_init();
     }
-    if (warp == 8) {
+    if (warp == kRoleWarp) {
         tmem_alloc(&sh.tmem_base, 512);
         tmem_relinquish();
     }
@@ -57,23 +57,25 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward(const __grid_co
     tc_fence_after();
     const uint32_t tmem = sh.tmem_base;
 
-    if (warp >= 8) {
-        reg_dealloc<96>();
-        if (warp <= 9) {
-            if (lane == 0) mma_role<D, BF16, KV>(p, w, sh, tmem, s_owner, s_ring, warp - 8);
-        } else if (warp == 10) {
+    // With two consumer warpgroups (384 threads, 168 registers at launch) registers move from the role
+    // warpgroup to the consumers; with four (640 threads, 96 registers) every role fits as launched.
+    if (warp >= kRoleWarp) {
+        if (kGroups == 2) reg_dealloc<96>();
+        if (warp <= kRoleWarp + 1) {
+            if (lane == 0) mma_role<D, BF16, KV>(p, w, sh, tmem, s_owner, s_ring, warp - kRoleWarp);
+        } else if (warp == kRoleWarp + 2) {
             if (lane == 0) loader_role<D, KV>(maps, p, w, sh, s_owner, s_ring);
         } else {
             if (KV) stats_role<KV>(p, w, sh, s_stats, lane);
         }
     } else {
-        reg_alloc<200>();
+        if (kGroups == 2) reg_alloc<200>();
         consumer_role<D, BF16, KV>(p, w, sh, tmem, s_stats, warp >> 2, warp, lane);
     }
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 2000 + sh.abort_word;
-    if (warp == 8) tmem_dealloc(tmem, 512);
+    if (warp == kRoleWarp) tmem_dealloc(tmem, 512);
 }
 
 // delta[row] = sum_d O * dO with coalesced 16-byte loads: D/8 threads per row.

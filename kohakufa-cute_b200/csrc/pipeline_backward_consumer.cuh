@@ -1,7 +1,7 @@
 // Consumer warpgroups of the backward pipeline: scores -> P -> dS, and the gradient epilogue.
 //
-// A consumer thread owns one owner row (tensor-memory lane) and 32 of the 64 columns of every
-// sub-tile (warpgroup 0 the first 32, warpgroup 1 the rest).  Per element, in FP32:
+// A consumer thread owns one owner row (tensor-memory lane) and 64 / kGroups of the 64 columns of
+// every sub-tile (warpgroup g takes columns [g*kCols, (g+1)*kCols)).  Per element, in FP32:
 //   P      = ex2((s' - m) * |scale| * log2e - logsum)      s' arrives already sign-adjusted
 //   P_low  = round(P)                                       one rounding to the input type
 //   dS_low = round(P_low * (dP - delta))
@@ -39,8 +39,7 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
         if (row_m == -INFINITY) row_m = INFINITY;  // nothing visible: every P is zero
     }
 
-    // Both warpgroups work on every sub-tile: this one takes columns [wg*32, wg*32+32) of the 64.
-    constexpr int kCols = kSub / 2;
+    // Every consumer warpgroup works on every sub-tile: this one takes columns [wg*kCols, (wg+1)*kCols).
     int g, i;
     w.begin(p, g, i);
     int unit = 0;
@@ -56,8 +55,8 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
             tc_fence_after();
             const uint32_t s_addr = lane_base + sub * 128 + wg * kCols, dp_addr = s_addr + 64;
             uint32_t s[kCols], dp[kCols];
-            tmem_ld32(s_addr, s);
-            tmem_ld32(dp_addr, dp);
+            tmem_ld(s_addr, s);
+            tmem_ld(dp_addr, dp);
             tmem_wait_ld();
             KFA_TRACE_POINT(1 + wg, 3);
 
@@ -126,8 +125,8 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
             }
             // P_low over the head of this thread's S columns (key owners only), dS_low over its dP columns
             KFA_TRACE_POINT(1 + wg, 4);
-            if (KV) tmem_st16(s_addr, pw);
-            tmem_st16(dp_addr, dw);
+            if (KV) tmem_st(s_addr, pw);
+            tmem_st(dp_addr, dw);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&sh.done[sub]);
@@ -139,8 +138,8 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
     }
 
     // ---------------------------------------------------------------- epilogue
-    // Each warpgroup stores half of the channels of every gradient row.
-    constexpr int kHalf = D / 2;
+    // Each warpgroup stores D / kGroups channels of every gradient row.
+    constexpr int kHalf = D / kGroups;
     const int ch0 = wg * kHalf;
     T* out1 = nullptr;  // dQ or dK (scaled)
     T* out2 = nullptr;  // dV
@@ -171,14 +170,15 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
         const uint32_t acc = lane_base + (which == 0 ? 384 : 256) + ch0;
         T* out = which == 0 ? out1 : out2;
         const float mul = which == 0 ? p.scale : 1.f;
+        constexpr int kStep = kHalf < 32 ? 16 : 32;
 #pragma unroll
-        for (int c = 0; c < kHalf; c += 32) {
-            uint32_t v[32];
-            tmem_ld32(acc + c, v);
+        for (int c = 0; c < kHalf; c += kStep) {
+            uint32_t v[kStep];
+            tmem_ld(acc + c, v);
             tmem_wait_ld();
             if (out) {
 #pragma unroll
-                for (int e = 0; e < 32; e += 8) {
+                for (int e = 0; e < kStep; e += 8) {
                     uint4 o;
                     o.x = pack2<BF16>(__uint_as_float(v[e]) * mul, __uint_as_float(v[e + 1]) * mul);
                     o.y = pack2<BF16>(__uint_as_float(v[e + 2]) * mul, __uint_as_float(v[e + 3]) * mul);

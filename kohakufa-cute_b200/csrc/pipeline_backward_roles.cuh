@@ -9,7 +9,7 @@
 //               every query head in the group; it produces dK = (sum dS_low^T Q) * scale and
 //               dV = sum P_low^T dO.  One owner per output row, so no atomics are needed.
 // Each streamed 128-row tile is processed as two 64-wide sub-tiles in two tensor-memory buffers:
-// while the two consumer warpgroups turn one sub-tile's scores into P and dS (32 columns each),
+// while the consumer warpgroups turn one sub-tile's scores into P and dS (64 / kGroups columns each),
 // the tensor core works on the other sub-tile.  Per sub-tile the tensor core runs
 //   S  = A1 x B1^T   (A1 = owner operand 1: Q or K;  B1 = streamed operand 1: K or Q)
 //   dP = A2 x B2^T   (A2 = owner operand 2: dO or V; B2 = streamed operand 2: V or dO)
@@ -28,7 +28,14 @@ namespace bwd {
 
 constexpr int kTile = 128;     // owner rows, and rows of a streamed tile
 constexpr int kSub = 64;       // columns of one sub-tile
-constexpr int kThreads = 384;  // consumer WG 0, consumer WG 1, (MMA issuer 0, MMA issuer 1, loader, statistics)
+#ifndef KFA_BWD_CONSUMER_GROUPS
+#define KFA_BWD_CONSUMER_GROUPS 4
+#endif
+constexpr int kGroups = KFA_BWD_CONSUMER_GROUPS;  // consumer warpgroups; each takes 64 / kGroups columns of a sub-tile
+constexpr int kCols = kSub / kGroups;
+constexpr int kConsumers = 128 * kGroups;
+constexpr int kRoleWarp = 4 * kGroups;            // first warp of the role warpgroup: MMA 0, MMA 1, loader, statistics
+constexpr int kThreads = kConsumers + 128;
 constexpr int kMaxPairs = 4;
 
 template <int D>
@@ -209,8 +216,8 @@ __device__ __forceinline__ void mma_role(const AttnParams& p, const Work<KV>& w,
 #pragma unroll
         for (int kk = 0; kk < kSub / 16; ++kk) {
             const uint32_t rows = (sub * 4 + kk) * 2048;  // 16 streamed rows per step, 128 bytes each
-            // each consumer warpgroup packs its 32 columns into the first 16 columns of its own range
-            const uint32_t a_off = (kk >> 1) * 32 + (kk & 1) * 8;
+            // each consumer warpgroup packs its kCols columns into the first kCols/2 columns of its own range
+            const uint32_t a_off = ((kk * 16) / kCols) * kCols + ((kk * 16) % kCols) / 2;
             umma_ts(grad_col, a_col + a_off, umma_desc_advance(ring_mn_desc, st + rows), idesc_g,
                     accumulate || kk > 0);
         }

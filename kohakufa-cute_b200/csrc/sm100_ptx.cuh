@@ -203,6 +203,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -228,6 +233,21 @@ template <int N>
 __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N>
 __device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+// Size-dispatched forms (the column count is the array length).
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[N]) {
+    static_assert(N == 16 || N == 32, "supported tensor-memory load widths");
+    if constexpr (N == 32) tmem_ld32(taddr, r);
+    else tmem_ld16(taddr, r);
+}
+template <int N>
+__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[N]) {
+    static_assert(N == 8 || N == 16 || N == 32, "supported tensor-memory store widths");
+    if constexpr (N == 32) tmem_st32(taddr, r);
+    else if constexpr (N == 16) tmem_st16(taddr, r);
+    else tmem_st8(taddr, r);
+}
 
 // Named barrier among a subset of the CTA's warps.
 __device__ __forceinline__ void bar_sync(int id, int threads) {
