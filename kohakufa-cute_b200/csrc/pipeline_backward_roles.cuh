@@ -29,7 +29,7 @@ namespace bwd {
 constexpr int kTile = 128;     // owner rows, and rows of a streamed tile
 constexpr int kSub = 64;       // columns of one sub-tile
 #ifndef KFA_BWD_CONSUMER_GROUPS
-#define KFA_BWD_CONSUMER_GROUPS 4
+#define KFA_BWD_CONSUMER_GROUPS 2
 #endif
 constexpr int kGroups = KFA_BWD_CONSUMER_GROUPS;  // consumer warpgroups; each takes 64 / kGroups columns of a sub-tile
 constexpr int kCols = kSub / kGroups;
