@@ -49,7 +49,7 @@ def sources():
 
 def build(force=False, verbose=True):
     os.makedirs(OBJ_DIR, exist_ok=True)
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".inl"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "kfa.h"))
     objects, jobs = [], []
     for src in sources():

@@ -67,21 +67,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Poll budget of a bounded wait. The first polls are back to back; later ones
-// sleep, so the whole budget is on the order of a second of wall time.
-constexpr uint32_t kFastPolls = 2048;
-constexpr uint32_t kSlowPolls = 4u << 20;
+// Budget of a bounded wait, in SM clock cycles (about two seconds).  The wait polls back to back:
+// a sleeping poll loop costs several hundred cycles of wake-up latency per hand-off, which the
+// pipelines pay on every tile.
+constexpr long long kWaitCycles = 4000000000LL;
 
 // Waits for the phase with the given parity. Returns false when the CTA has
 // been aborted (by this wait running out, or by another role).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word, int where) {
     if (mbar_try_wait(bar, parity)) return true;
-    for (uint32_t i = 0; i < kFastPolls; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    for (uint32_t i = 0; i < kSlowPolls; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
         if (*abort_word != 0) return false;
-        __nanosleep(200);
+        if (clock64() - start > kWaitCycles) break;
     }
     *abort_word = where;
     return false;
