@@ -48,17 +48,17 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
         if (KV) ok = mbar_wait(&sh.stats_full[unit & 1], (unit >> 1) & 1, abort_word, 140);
         const int state = KV ? 2 : key_tile_state(p, w.b, w.head, i);
         for (int sub = 0; sub < 2 && ok; ++sub) {
-            KFA_TRACE_POINT(1 + wg, 1);
+            KFA_TRACE_POINT(1, 1);
             ok = mbar_wait(&sh.sdp_ready[sub], unit & 1, abort_word, 141 + sub);
             if (!ok) break;
-            KFA_TRACE_POINT(1 + wg, 2);
+            KFA_TRACE_POINT(1, 2);
             tc_fence_after();
             const uint32_t s_addr = lane_base + sub * 128 + wg * kCols, dp_addr = s_addr + 64;
             uint32_t s[kCols], dp[kCols];
             tmem_ld(s_addr, s);
             tmem_ld(dp_addr, dp);
             tmem_wait_ld();
-            KFA_TRACE_POINT(1 + wg, 3);
+            KFA_TRACE_POINT(1, 3);
 
             // columns [lo, hi) of this thread's 32 are visible
             const int col0 = i * kTile + sub * kSub + wg * kCols;  // first streamed row (key or query)
@@ -124,13 +124,13 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
                 for (int c = 0; c < kCols; c += 2) pair(c, false);
             }
             // P_low over the head of this thread's S columns (key owners only), dS_low over its dP columns
-            KFA_TRACE_POINT(1 + wg, 4);
+            KFA_TRACE_POINT(1, 4);
             if (KV) tmem_st(s_addr, pw);
             tmem_st(dp_addr, dw);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&sh.done[sub]);
-            KFA_TRACE_POINT(1 + wg, 5);
+            KFA_TRACE_POINT(1, 5);
         }
         if (KV && ok) mbar_arrive(&sh.stats_empty[unit & 1]);
         w.next(p, g, i);

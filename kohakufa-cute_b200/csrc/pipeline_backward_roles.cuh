@@ -236,13 +236,13 @@ __device__ __forceinline__ void mma_role(const AttnParams& p, const Work<KV>& w,
         const bool more = w.valid(gn);
         const int slot = unit % C::kPairs, nslot = (unit + 1) % C::kPairs;
         for (int sub = 0; sub < 2 && ok; ++sub) {
-            KFA_TRACE_POINT(0, 1);
+            KFA_TRACE_POINT(chain * 2, 1);
             ok = mbar_wait(&sh.done[sub], unit & 1, abort_word, 122 + sub);
             if (!ok) break;
-            KFA_TRACE_POINT(0, 2);
+            KFA_TRACE_POINT(chain * 2, 2);
             tc_fence_after();
             if (has_grad) issue_grads(slot, sub, unit > 0 || sub > 0);
-            KFA_TRACE_POINT(0, 3);
+            KFA_TRACE_POINT(chain * 2, 3);
             if (sub == 1) umma_commit(&sh.pair_empty[slot]);
             if (more) {
                 if (sub == 0) {
@@ -251,7 +251,7 @@ __device__ __forceinline__ void mma_role(const AttnParams& p, const Work<KV>& w,
                     tc_fence_after();
                 }
                 issue_scores(nslot, sub);
-                KFA_TRACE_POINT(0, 4);
+                KFA_TRACE_POINT(chain * 2, 4);
             }
         }
         g = gn;
