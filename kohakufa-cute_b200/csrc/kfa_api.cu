@@ -290,6 +290,29 @@ void kfa_profile_reset(void) {
     g_totals.clear();
 }
 
+}  // extern "C"
+
+namespace {
+
+size_t delta_bytes(const kfa_tensor* q) {
+    const size_t rows = (size_t)q->sizes[0] * q->sizes[1] * q->sizes[2];
+    return ((rows * sizeof(float) + 255) / 256) * 256;
+}
+
+// Scratch of the wide-head backward behind the delta rows: the P_low and dS_low matrices.  Zero when
+// the head is not wide or the matrices would exceed 8 GiB (the general kernels run then).
+size_t wide_extra_bytes(const kfa_tensor* q, const kfa_tensor* k) {
+    if (!q || !k || q->ndim != 4 || k->ndim != 4) return 0;
+    const int64_t D = q->sizes[3];
+    if (D != 256 && D != 384 && D != 512) return 0;
+    const size_t one = kfa::wide_stored_bytes(q->sizes[0], q->sizes[1], q->sizes[2], k->sizes[2]);
+    return one <= (size_t(4) << 30) ? 2 * one : 0;
+}
+
+}  // namespace
+
+extern "C" {
+
 int kfa_selected_family(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
                         int causal, int backward) {
     if (check_qkv(q, k, v)) return -1;
@@ -307,8 +330,12 @@ int kfa_selected_family(const kfa_tensor* q, const kfa_tensor* k, const kfa_tens
     p.dv = const_cast<void*>(v->data);
     copy4(p.dvs, v->strides);
     const bool bf16 = q->dtype == KFA_BF16;
-    return backward ? (kfa::pipeline_backward_supported(p, bf16) ? 1 : 0)
-                    : (kfa::pipeline_forward_supported(p, bf16) ? 1 : 0);
+    if (backward) {
+        if (kfa::pipeline_backward_supported(p, bf16)) return 1;
+        return kfa::wide_backward_supported(p) && wide_extra_bytes(q, k) > 0 ? 2 : 0;
+    }
+    if (kfa::pipeline_forward_supported(p, bf16)) return 1;
+    return kfa::wide_forward_supported(p) ? 2 : 0;
 }
 
 int kfa_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
@@ -337,6 +364,9 @@ int kfa_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, c
     if (kfa::pipeline_forward_supported(p, bf16)) {
         ce = timed("pipeline_forward", st, [&] { return kfa::launch_pipeline_forward(p, bf16, st); });
         if (ce != cudaSuccess) return cuda_fail(ce, "pipeline forward launch");
+    } else if (kfa::wide_forward_supported(p)) {
+        ce = timed("wide_forward", st, [&] { return kfa::launch_wide_forward(p, bf16, st); });
+        if (ce != cudaSuccess) return cuda_fail(ce, "wide-head forward launch");
     } else {
         ce = timed("general_forward", st, [&] { return kfa::launch_general_forward(p, bf16, st); });
         if (ce != cudaSuccess) return cuda_fail(ce, "general forward launch");
@@ -369,10 +399,8 @@ int kfa_pack_mask(const kfa_tensor* mask, kfa_tensor* blocks, void* stream) {
 }
 
 size_t kfa_backward_workspace_bytes(const kfa_tensor* q, const kfa_tensor* k) {
-    (void)k;
     if (!q || q->ndim != 4) return 0;
-    const size_t rows = (size_t)q->sizes[0] * q->sizes[1] * q->sizes[2];
-    return ((rows * sizeof(float) + 255) / 256) * 256;
+    return delta_bytes(q) + wide_extra_bytes(q, k);
 }
 
 int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
@@ -409,6 +437,7 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool bf16 = q->dtype == KFA_BF16;
     const bool pipeline = kfa::pipeline_backward_supported(p, bf16);
+    const bool wide = !pipeline && kfa::wide_backward_supported(p) && wide_extra_bytes(q, k) > 0;
     cudaError_t ce = timed("output_delta", st, [&] {
         return pipeline ? kfa::launch_pipeline_delta(p, bf16, st) : kfa::launch_output_delta(p, bf16, st);
     });
@@ -418,6 +447,14 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
         if (ce != cudaSuccess) return cuda_fail(ce, "pipeline backward (dQ) launch");
         ce = timed("pipeline_backward_kv", st, [&] { return kfa::launch_pipeline_backward(p, bf16, 1, st); });
         if (ce != cudaSuccess) return cuda_fail(ce, "pipeline backward (dK/dV) launch");
+    } else if (wide) {
+        void* stored = static_cast<char*>(workspace) + delta_bytes(q);
+        static const char* const names[5] = {"wide_scores_p", "wide_scores_ds", "wide_grad_q", "wide_grad_k",
+                                             "wide_grad_v"};
+        for (int step = 0; step < 5; ++step) {
+            ce = timed(names[step], st, [&] { return kfa::launch_wide_backward(p, bf16, step, stored, st); });
+            if (ce != cudaSuccess) return cuda_fail(ce, "wide-head backward launch");
+        }
     } else {
         ce = timed("general_backward_q", st, [&] { return kfa::launch_general_backward(p, bf16, 0, st); });
         if (ce != cudaSuccess) return cuda_fail(ce, "general backward (dQ) launch");

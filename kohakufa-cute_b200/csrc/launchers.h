@@ -25,6 +25,15 @@ cudaError_t launch_pipeline_forward(const AttnParams& p, bool bf16, cudaStream_t
 bool pipeline_backward_supported(const AttnParams& p, bool bf16);
 cudaError_t launch_pipeline_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st);
 cudaError_t launch_pipeline_delta(const AttnParams& p, bool bf16, cudaStream_t st);
+
+// Wide heads (256/384/512 channels) on the tensor-memory pipeline.  The backward needs two 16-bit
+// [B,Hq,Sq,ceil128(Sk)] matrices (`wide_stored_bytes` each) behind the delta scratch.
+bool wide_forward_supported(const AttnParams& p);
+cudaError_t launch_wide_forward(const AttnParams& p, bool bf16, cudaStream_t st);
+size_t wide_stored_bytes(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk);
+bool wide_backward_supported(const AttnParams& p);
+cudaError_t launch_wide_backward(const AttnParams& p, bool bf16, int step, void* stored, cudaStream_t st);
+
 int pipeline_configured_variants();
 void pipeline_forget_variants();
 

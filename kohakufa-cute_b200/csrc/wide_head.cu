@@ -1,0 +1,802 @@
+// Wide heads (256, 384 or 512 channels) on the Blackwell tensor-memory pipeline.
+//
+// A 128-row accumulator with 512 FP32 channels fills the whole tensor memory of an SM, and two
+// 128 x 512 operands do not fit its shared memory, so the narrow-head kernels do not scale up.
+// This family splits the work differently:
+//
+//   wide_forward   a CTA owns 128 query rows and ONE HALF of the output channels.  It forms the
+//                  full score tile S = Q K^T (Q resident, K streamed as 64-channel chunks), runs
+//                  the shifted-score online softmax, and accumulates O[:, half] = P V[:, half].
+//                  The sibling CTA repeats the scores for the other half (1.5x the algorithmic
+//                  tensor work, no exchange between CTAs).
+//   wide_scores    backward, step 1 and 2: P_low = rd(ex2((s'-m)c - logsum)) and
+//                  dS_low = rd(P_low (dP - delta)) are written ONCE as 16-bit matrices
+//                  [B, Hq, Sq, Sk] into the caller's workspace (Q resident / K streamed for P,
+//                  dO resident / V streamed for dS).  Hidden entries are exact zeros.
+//   wide_grad      backward, step 3: dQ = dS_low K, dK = dS_low^T Q, dV = P_low^T dO as plain
+//                  tensor-core products over the stored matrices; a CTA owns 128 output rows and
+//                  one half of the channels, so no score is recomputed and no atomics are needed.
+//
+// The arithmetic is the operator's contract (reference behaviour:
+// src/kohakufa_cute/blackwell_pipeline.py:141-209, 610-662 and docs/precision.md:13-23 of the
+// reference project): P_low and dS_low are rounded once - exactly the values that are stored -
+// every product accumulates in FP32, and the signed scale is applied after accumulation.
+#include "kfa_common.cuh"
+#include "launchers.h"
+#include "sm100_ptx.cuh"
+#include "tensor_map.h"
+
+#include <type_traits>
+
+namespace kfa {
+namespace {
+
+constexpr int kTile = 128;
+constexpr int kChunkBytes = kTile * 128;  // 128 rows x 64 channels of a 16-bit type (one TMA box)
+constexpr int kRing = 6;                  // 16 KB slots for streamed chunks
+constexpr float kRebase = 8.0f;
+
+// Combined state of key tile j (128 keys) from the 64-key table entries: 0 hidden, 2 visible, 1 mixed.
+__device__ __forceinline__ int key_tile_state(const AttnParams& p, int b, int h, int j) {
+    if (!p.has_mask) return 2;
+    const int nk64 = (p.Sk + 63) >> 6;
+    const int32_t* base = p.blocks + (int64_t)b * p.bs[0] + (int64_t)h * p.bs[1];
+    const int s0 = base[(int64_t)(2 * j) * p.bs[3]];
+    const int s1 = (2 * j + 1 < nk64) ? base[(int64_t)(2 * j + 1) * p.bs[3]] : s0;
+    if (s0 == 0 && s1 == 0) return 0;
+    if (s0 == 2 && s1 == 2) return 2;
+    return 1;
+}
+
+// Key tiles a 128-row query tile starting at q0 may see.
+__device__ __forceinline__ int key_tiles_of(const AttnParams& p, int q0) {
+    const int row_hi = min(p.Sq, q0 + kTile);
+    const int k_hi = p.causal ? min(p.Sk, row_hi) : p.Sk;
+    return (k_hi + kTile - 1) / kTile;
+}
+
+struct WideMaps {
+    CUtensorMap a, b, c;
+};
+
+// ------------------------------------------------------------------------------------------ forward
+struct FwdShared {
+    uint64_t q_full;
+    uint64_t full[kRing];
+    uint64_t empty[kRing];
+    uint64_t s_ready;
+    uint64_t p_ready;
+    uint32_t tmem_base;
+    int abort_word;
+};
+
+// maps.a = Q, maps.b = K, maps.c = V.  256 threads: warps 0-3 softmax (thread <-> query row),
+// warp 4 MMA issuer, warp 5 loader.  Tensor memory: S at column 0 (P_low overwrites its first 64
+// columns), O[:, half] at column 256.
+template <bool BF16>
+__global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ WideMaps maps, AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int chunks = p.D >> 6, hc = chunks >> 1;
+    uint8_t* sQ = smem;
+    uint8_t* sRing = smem + chunks * kChunkBytes;
+    FwdShared& sh = *reinterpret_cast<FwdShared*>(sRing + kRing * kChunkBytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int half = blockIdx.x & 1;
+    const int64_t rest = blockIdx.x >> 1;
+    const int nblk = (p.Sq + kTile - 1) / kTile;
+    const int qblk = nblk - 1 - (int)(rest % nblk);  // heavy (late) causal tiles first
+    const int64_t bh = rest / nblk;
+    const int h = (int)(bh % p.Hq), b = (int)(bh / p.Hq);
+    const int kvh = h / p.group;
+    const int q0 = qblk * kTile;
+    const int n_tiles = key_tiles_of(p, q0);
+
+    if (threadIdx.x == 0) {
+        sh.abort_word = 0;
+        mbar_init(&sh.q_full, 1);
+        for (int i = 0; i < kRing; ++i) {
+            mbar_init(&sh.full[i], 1);
+            mbar_init(&sh.empty[i], 1);
+        }
+        mbar_init(&sh.s_ready, 1);
+        mbar_init(&sh.p_ready, kTile);
+        mbar_fence_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(&sh.tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    volatile int* abort_word = &sh.abort_word;
+
+    if (warp == 5) {
+        // ---------------------------------------------------------------- loader
+        if (lane == 0) {
+            tma_prefetch_desc(&maps.a);
+            tma_prefetch_desc(&maps.b);
+            tma_prefetch_desc(&maps.c);
+            mbar_expect_tx(&sh.q_full, chunks * kChunkBytes);
+            for (int c = 0; c < chunks; ++c) tma_load_4d(sQ + c * kChunkBytes, &maps.a, &sh.q_full, c * 64, q0, h, b);
+            int pos = 0;
+            bool ok = true;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (key_tile_state(p, b, h, j) == 0) continue;
+                // the K chunks of the tile, then the V chunks of this CTA's channel half
+                for (int i = 0; i < chunks + hc && ok; ++i, ++pos) {
+                    const int slot = pos % kRing, round = pos / kRing;
+                    if (round > 0) ok = mbar_wait(&sh.empty[slot], (round - 1) & 1, abort_word, 10);
+                    if (!ok) break;
+                    mbar_expect_tx(&sh.full[slot], kChunkBytes);
+                    if (i < chunks)
+                        tma_load_4d(sRing + slot * kChunkBytes, &maps.b, &sh.full[slot], i * 64, j * kTile, kvh, b);
+                    else
+                        tma_load_4d(sRing + slot * kChunkBytes, &maps.c, &sh.full[slot],
+                                    (half * hc + i - chunks) * 64, j * kTile, kvh, b);
+                }
+            }
+        }
+    } else if (warp == 4) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_s =
+                umma_idesc(kTile, kTile, BF16 ? 1 : 0, false, false) | (p.scale < 0.f ? kUmmaNegateA : 0u);
+            const uint32_t idesc_o = umma_idesc(kTile, 64 * hc, BF16 ? 1 : 0, false, true);
+            const uint64_t q_desc = umma_desc_sw128(smem_u32(sQ), 16, 1024);
+            const uint64_t k_desc = umma_desc_sw128(smem_u32(sRing), 16, 1024);
+            // V chunks of one tile sit in consecutive slots: N = 64 * hc channels per instruction
+            const uint64_t v_desc = umma_desc_sw128(smem_u32(sRing), kChunkBytes, 1024);
+            bool ok = mbar_wait(&sh.q_full, 0, abort_word, 20);
+            int pos = 0, iter = 0;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (key_tile_state(p, b, h, j) == 0) continue;
+                for (int c = 0; c < chunks && ok; ++c, ++pos) {
+                    const int slot = pos % kRing;
+                    ok = mbar_wait(&sh.full[slot], (pos / kRing) & 1, abort_word, 21);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_ss(tmem, umma_desc_advance(q_desc, c * kChunkBytes + kk * 32),
+                                umma_desc_advance(k_desc, slot * kChunkBytes + kk * 32), idesc_s, c > 0 || kk > 0);
+                    umma_commit(&sh.empty[slot]);
+                }
+                if (!ok) break;
+                umma_commit(&sh.s_ready);
+                const int s0 = pos % kRing;
+                for (int i = 0; i < hc && ok; ++i)
+                    ok = mbar_wait(&sh.full[(pos + i) % kRing], ((pos + i) / kRing) & 1, abort_word, 22);
+                if (ok) ok = mbar_wait(&sh.p_ready, iter & 1, abort_word, 23);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk)
+                    umma_ts(tmem + 256, tmem + kk * 8, umma_desc_advance(v_desc, s0 * kChunkBytes + kk * 2048), idesc_o,
+                            iter > 0 || kk > 0);
+                for (int i = 0; i < hc; ++i) umma_commit(&sh.empty[(pos + i) % kRing]);
+                pos += hc;
+                ++iter;
+            }
+            if (ok) umma_commit(&sh.s_ready);  // completion of the last product
+        }
+    } else if (warp < 4) {
+        // --------------------------------------------------------------- softmax
+        using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+        const int row = q0 + warp * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        const uint32_t s_addr = lane_base, o_addr = lane_base + 256;
+        const int width = 64 * hc;  // output channels of this CTA
+        const float c2 = fabsf(p.scale) * kLog2e;
+        const uint64_t c2_pair = f2_pack(c2, c2);
+        const uint8_t* kmask = p.has_mask ? p.mask + (int64_t)b * p.ms[0] + (int64_t)h * p.ms[1] : nullptr;
+        float m_used = -INFINITY, m_true = -INFINITY, l = 0.f;
+        int iter = 0;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int state = key_tile_state(p, b, h, j);
+            if (state == 0) continue;
+            ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 30);
+            if (!ok) break;
+            tc_fence_after();
+            float s[kTile];
+#pragma unroll
+            for (int c = 0; c < kTile; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(s_addr + c, r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(r[i]);
+            }
+            tmem_wait_ld();
+            const int key0 = j * kTile;
+            int lim = p.Sk - key0;
+            if (p.causal) lim = min(lim, row - key0 + 1);
+            if (lim < kTile) {
+#pragma unroll
+                for (int c = 0; c < kTile; ++c) s[c] = c < lim ? s[c] : -INFINITY;
+            }
+            if (state == 1) {
+#pragma unroll
+                for (int c = 0; c < kTile; ++c) {
+                    const int key = min(key0 + c, p.Sk - 1);
+                    s[c] = kmask[(int64_t)key * p.ms[3]] != 0 ? s[c] : -INFINITY;
+                }
+            }
+            float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
+#pragma unroll
+            for (int c = 6; c < kTile - 2; c += 4) {
+                mx0 = max3(mx0, s[c], s[c + 1]);
+                mx1 = max3(mx1, s[c + 2], s[c + 3]);
+            }
+            const float mx = max3(mx0, mx1, fmaxf(s[kTile - 2], s[kTile - 1]));
+            m_true = fmaxf(m_true, mx);
+            const bool rebase = mx > m_used && (m_used == -INFINITY || (mx - m_used) * c2 > kRebase);
+            float alpha = 1.f;
+            if (rebase) {
+                alpha = (m_used == -INFINITY) ? 0.f : ex2((m_used - mx) * c2);
+                l *= alpha;
+                m_used = mx;
+            }
+            // s_ready of this tile was committed after the previous product, so O is quiescent here
+            if (iter > 0 && __any_sync(0xffffffffu, rebase)) {
+                for (int c = 0; c < width; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(o_addr + c, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    tmem_st32(o_addr + c, r);
+                }
+            }
+            const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+            const uint64_t m_pair = f2_pack(m_safe, m_safe);
+            uint64_t sum_a = f2_pack(0.f, 0.f), sum_b = sum_a;
+#pragma unroll
+            for (int c = 0; c < kTile; c += 32) {
+                uint32_t w[16];
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    float pa, pb, pc, pd;
+                    f2_unpack(f2_mul(f2_sub(f2_pack(s[c + 2 * i], s[c + 2 * i + 1]), m_pair), c2_pair), pa, pb);
+                    f2_unpack(f2_mul(f2_sub(f2_pack(s[c + 2 * i + 2], s[c + 2 * i + 3]), m_pair), c2_pair), pc, pd);
+                    pa = ex2(pa);
+                    pb = ex2(pb);
+                    pc = ex2(pc);
+                    pd = ex2(pd);
+                    sum_a = f2_add(sum_a, f2_pack(pa, pb));
+                    sum_b = f2_add(sum_b, f2_pack(pc, pd));
+                    w[i] = pack2<BF16>(pa, pb);
+                    w[i + 1] = pack2<BF16>(pc, pd);
+                }
+                tmem_st16(s_addr + c / 2, w);
+            }
+            {
+                float x0, x1, x2, x3;
+                f2_unpack(sum_a, x0, x1);
+                f2_unpack(sum_b, x2, x3);
+                l += (x0 + x1) + (x2 + x3);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sh.p_ready);
+            ++iter;
+        }
+        T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] + (int64_t)row * p.os[2] +
+                  half * width;
+        const int64_t si = ((int64_t)b * p.Hq + h) * p.Sq + row;
+        if (ok && iter == 0 && row < p.Sq) {
+            // every key tile of this row is hidden: zero output, empty statistics
+            for (int d = 0; d < width; d += 8) *reinterpret_cast<uint4*>(orow + d) = make_uint4(0, 0, 0, 0);
+            if (half == 0) {
+                p.maximum[si] = -INFINITY;
+                p.logsum[si] = 0.f;
+            }
+        }
+        if (iter > 0) {
+            if (ok) ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 31);
+            if (ok) {
+                tc_fence_after();
+                const float den = l > 0.f ? l : 1.f;
+                for (int c = 0; c < width; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(o_addr + c, r);
+                    tmem_wait_ld();
+                    if (row < p.Sq) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 w;
+                            w.x = pack2<BF16>(__uint_as_float(r[i]) / den, __uint_as_float(r[i + 1]) / den);
+                            w.y = pack2<BF16>(__uint_as_float(r[i + 2]) / den, __uint_as_float(r[i + 3]) / den);
+                            w.z = pack2<BF16>(__uint_as_float(r[i + 4]) / den, __uint_as_float(r[i + 5]) / den);
+                            w.w = pack2<BF16>(__uint_as_float(r[i + 6]) / den, __uint_as_float(r[i + 7]) / den);
+                            *reinterpret_cast<uint4*>(orow + c + i) = w;
+                        }
+                    }
+                }
+                if (row < p.Sq && half == 0) {
+                    p.maximum[si] = m_true;
+                    p.logsum[si] = l > 0.f ? log2f(l) + (m_used - m_true) * c2 : 0.f;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 3000 + sh.abort_word;
+    if (warp == 4) tmem_dealloc(tmem, 512);
+}
+
+// ------------------------------------------------------------------------- backward: P and dS matrices
+// The stored matrices: 16-bit [B, Hq, Sq, pitch] with pitch = Sk rounded up to 128.
+struct Stored {
+    void* p_low;
+    void* ds_low;
+    int64_t pitch;
+};
+
+struct ScoreShared {
+    uint64_t own_full;
+    uint64_t full[kRing];
+    uint64_t empty[kRing];
+    uint64_t s_ready[2];
+    uint64_t s_free[2];
+    uint32_t tmem_base;
+    int abort_word;
+};
+
+// MODE 0: maps.a = Q (resident), maps.b = K (streamed); writes P_low.
+// MODE 1: maps.a = dO (resident), maps.b = V (streamed); reads P_low, writes dS_low.
+// 256 threads: warps 0-3 consumers (thread <-> query row), warp 4 MMA issuer, warp 5 loader.
+// Two score buffers in tensor memory (columns 0 and 128) let the tensor core run one tile ahead.
+template <int MODE, bool BF16>
+__global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ WideMaps maps, AttnParams p, Stored st) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int chunks = p.D >> 6;
+    uint8_t* sOwn = smem;
+    uint8_t* sRing = smem + chunks * kChunkBytes;
+    ScoreShared& sh = *reinterpret_cast<ScoreShared*>(sRing + kRing * kChunkBytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nblk = (p.Sq + kTile - 1) / kTile;
+    const int qblk = nblk - 1 - (int)(blockIdx.x % nblk);
+    const int64_t bh = blockIdx.x / nblk;
+    const int h = (int)(bh % p.Hq), b = (int)(bh / p.Hq);
+    const int kvh = h / p.group;
+    const int q0 = qblk * kTile;
+    const int n_tiles = key_tiles_of(p, q0);
+
+    if (threadIdx.x == 0) {
+        sh.abort_word = 0;
+        mbar_init(&sh.own_full, 1);
+        for (int i = 0; i < kRing; ++i) {
+            mbar_init(&sh.full[i], 1);
+            mbar_init(&sh.empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sh.s_ready[i], 1);
+            mbar_init(&sh.s_free[i], kTile);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(&sh.tmem_base, 256);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    volatile int* abort_word = &sh.abort_word;
+
+    if (warp == 5) {
+        if (lane == 0) {
+            tma_prefetch_desc(&maps.a);
+            tma_prefetch_desc(&maps.b);
+            mbar_expect_tx(&sh.own_full, chunks * kChunkBytes);
+            for (int c = 0; c < chunks; ++c)
+                tma_load_4d(sOwn + c * kChunkBytes, &maps.a, &sh.own_full, c * 64, q0, h, b);
+            int pos = 0;
+            bool ok = true;
+            for (int j = 0; j < n_tiles && ok; ++j)
+                for (int c = 0; c < chunks && ok; ++c, ++pos) {
+                    const int slot = pos % kRing, round = pos / kRing;
+                    if (round > 0) ok = mbar_wait(&sh.empty[slot], (round - 1) & 1, abort_word, 40);
+                    if (!ok) break;
+                    mbar_expect_tx(&sh.full[slot], kChunkBytes);
+                    tma_load_4d(sRing + slot * kChunkBytes, &maps.b, &sh.full[slot], c * 64, j * kTile, kvh, b);
+                }
+        }
+    } else if (warp == 4) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(kTile, kTile, BF16 ? 1 : 0, false, false) |
+                                   (MODE == 0 && p.scale < 0.f ? kUmmaNegateA : 0u);
+            const uint64_t a_desc = umma_desc_sw128(smem_u32(sOwn), 16, 1024);
+            const uint64_t b_desc = umma_desc_sw128(smem_u32(sRing), 16, 1024);
+            bool ok = mbar_wait(&sh.own_full, 0, abort_word, 41);
+            int pos = 0;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int buf = j & 1;
+                if (j >= 2) ok = mbar_wait(&sh.s_free[buf], ((j >> 1) - 1) & 1, abort_word, 42);
+                if (!ok) break;
+                tc_fence_after();
+                for (int c = 0; c < chunks && ok; ++c, ++pos) {
+                    const int slot = pos % kRing;
+                    ok = mbar_wait(&sh.full[slot], (pos / kRing) & 1, abort_word, 43);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_ss(tmem + buf * 128, umma_desc_advance(a_desc, c * kChunkBytes + kk * 32),
+                                umma_desc_advance(b_desc, slot * kChunkBytes + kk * 32), idesc, c > 0 || kk > 0);
+                    umma_commit(&sh.empty[slot]);
+                }
+                if (ok) umma_commit(&sh.s_ready[buf]);
+            }
+        }
+    } else if (warp < 4) {
+        const int row = q0 + warp * 32 + lane;
+        const bool row_ok = row < p.Sq;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        const float c2 = fabsf(p.scale) * kLog2e;
+        const uint64_t c2_pair = f2_pack(c2, c2);
+        const int64_t si = ((int64_t)b * p.Hq + h) * p.Sq + (row_ok ? row : 0);
+        float row_m = INFINITY, row_ls = 0.f, row_dl = 0.f;
+        if (row_ok) {
+            if (MODE == 0) {
+                row_m = p.maximum[si];
+                row_ls = p.logsum[si];
+                if (row_m == -INFINITY) row_m = INFINITY;  // nothing visible: every P is zero
+            } else {
+                row_dl = p.delta[si];
+            }
+        }
+        const uint8_t* kmask = p.has_mask ? p.mask + (int64_t)b * p.ms[0] + (int64_t)h * p.ms[1] : nullptr;
+        const int64_t row_off = (((int64_t)b * p.Hq + h) * p.Sq + (row_ok ? row : 0)) * st.pitch;
+        uint16_t* p_row = reinterpret_cast<uint16_t*>(st.p_low) + row_off;
+        uint16_t* ds_row = reinterpret_cast<uint16_t*>(st.ds_low) + row_off;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int buf = j & 1, key0 = j * kTile;
+            uint4 pl[16];
+            if (MODE == 1 && row_ok) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) pl[i] = *reinterpret_cast<const uint4*>(p_row + key0 + i * 8);
+            }
+            ok = mbar_wait(&sh.s_ready[buf], (j >> 1) & 1, abort_word, 44);
+            if (!ok) break;
+            tc_fence_after();
+            float s[kTile];
+#pragma unroll
+            for (int c = 0; c < kTile; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(lane_base + buf * 128 + c, r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(r[i]);
+            }
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&sh.s_free[buf]);
+            if (!row_ok) continue;
+            if (MODE == 0) {
+                int lim = p.Sk - key0;
+                if (p.causal) lim = min(lim, row - key0 + 1);
+                const int state = key_tile_state(p, b, h, j);
+                const uint64_t m_pair = f2_pack(row_m, row_m), l_pair = f2_pack(row_ls, row_ls);
+#pragma unroll
+                for (int c = 0; c < kTile; c += 8) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2) {
+                        float pa, pb;
+                        f2_unpack(f2_sub(f2_mul(f2_sub(f2_pack(s[c + i], s[c + i + 1]), m_pair), c2_pair), l_pair), pa,
+                                  pb);
+                        pa = ex2(pa);
+                        pb = ex2(pb);
+                        pa = c + i < lim ? pa : 0.f;
+                        pb = c + i + 1 < lim ? pb : 0.f;
+                        if (state != 2) {
+                            pa = kmask[(int64_t)min(key0 + c + i, p.Sk - 1) * p.ms[3]] != 0 ? pa : 0.f;
+                            pb = kmask[(int64_t)min(key0 + c + i + 1, p.Sk - 1) * p.ms[3]] != 0 ? pb : 0.f;
+                        }
+                        w[i / 2] = pack2<BF16>(pa, pb);
+                    }
+                    *reinterpret_cast<uint4*>(p_row + key0 + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            } else {
+                const uint64_t d_pair = f2_pack(row_dl, row_dl);
+#pragma unroll
+                for (int c = 0; c < kTile; c += 8) {
+                    const uint32_t in[4] = {pl[c / 8].x, pl[c / 8].y, pl[c / 8].z, pl[c / 8].w};
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2) {
+                        const float2 pv = unpack2<BF16>(in[i / 2]);
+                        float da, db;
+                        f2_unpack(f2_mul(f2_pack(pv.x, pv.y), f2_sub(f2_pack(s[c + i], s[c + i + 1]), d_pair)), da, db);
+                        // a hidden entry has P_low = 0; keep its gradient an exact zero whatever dP holds
+                        da = pv.x == 0.f ? 0.f : da;
+                        db = pv.y == 0.f ? 0.f : db;
+                        w[i / 2] = pack2<BF16>(da, db);
+                    }
+                    *reinterpret_cast<uint4*>(ds_row + key0 + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 3100 + sh.abort_word;
+    if (warp == 4) tmem_dealloc(tmem, 256);
+}
+
+// ------------------------------------------------------------------- backward: gradient products
+struct GradShared {
+    uint64_t full[2];
+    uint64_t empty[2];
+    uint64_t done;
+    uint32_t tmem_base;
+    int abort_word;
+};
+
+// WHICH 0: dQ[q tile] = scale * sum_kt dS_low[q tile, kt] K[kt]        (A K-major,  rows = queries)
+// WHICH 1: dK[k tile] = scale * sum_{g,i} dS_low[i, k tile]^T Q_g[i]   (A MN-major, rows = keys)
+// WHICH 2: dV[k tile] =         sum_{g,i} P_low[i, k tile]^T dO_g[i]
+// maps.a = the stored matrix, maps.b = K, Q or dO.  A CTA owns 128 output rows and one half of the
+// channels.  192 threads: warps 0-3 epilogue (thread <-> output row), warp 4 MMA issuer, warp 5
+// loader.  A stage holds one 128 x 128 block of the matrix (2 chunks) and 128 rows x D/2 channels
+// of the other operand.
+template <int WHICH, bool BF16>
+__global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ WideMaps maps, AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr bool KV = WHICH != 0;
+    const int hc = p.D >> 7;
+    const int stage_bytes = (2 + hc) * kChunkBytes;
+    GradShared& sh = *reinterpret_cast<GradShared*>(smem + 2 * stage_bytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int half = blockIdx.x & 1;
+    const int64_t rest = blockIdx.x >> 1;
+    const int owner_len = KV ? p.Sk : p.Sq, heads = KV ? p.Hkv : p.Hq;
+    const int nblk = (owner_len + kTile - 1) / kTile;
+    int blk = (int)(rest % nblk);
+    if (!KV) blk = nblk - 1 - blk;  // causal: late query tiles and early key tiles carry the most work
+    const int64_t bh = rest / nblk;
+    const int head = (int)(bh % heads), b = (int)(bh / heads);
+    const int owner0 = blk * kTile;
+    // streamed tile range and the number of passes over it (query heads of the group)
+    int first = 0, end, passes = 1;
+    if (KV) {
+        first = p.causal ? blk : 0;
+        end = (p.Sq + kTile - 1) / kTile;
+        passes = p.group;
+    } else {
+        end = key_tiles_of(p, owner0);
+    }
+    const int per_pass = max(end - first, 0);
+    const int units = per_pass * passes;
+
+    if (threadIdx.x == 0) {
+        sh.abort_word = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sh.full[i], 1);
+            mbar_init(&sh.empty[i], 1);
+        }
+        mbar_init(&sh.done, 1);
+        mbar_fence_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(&sh.tmem_base, 256);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    volatile int* abort_word = &sh.abort_word;
+
+    if (warp == 5) {
+        if (lane == 0 && units > 0) {
+            tma_prefetch_desc(&maps.a);
+            tma_prefetch_desc(&maps.b);
+            bool ok = true;
+            for (int u = 0; u < units && ok; ++u) {
+                const int g = u / per_pass, i = first + u % per_pass;
+                const int s = u & 1;
+                if (u >= 2) ok = mbar_wait(&sh.empty[s], ((u >> 1) - 1) & 1, abort_word, 50);
+                if (!ok) break;
+                uint8_t* dst = smem + s * stage_bytes;
+                mbar_expect_tx(&sh.full[s], stage_bytes);
+                const int hq = KV ? head * p.group + g : head;
+                const int q_row = KV ? i * kTile : owner0, k_col = KV ? owner0 : i * kTile;
+                for (int c = 0; c < 2; ++c)
+                    tma_load_4d(dst + c * kChunkBytes, &maps.a, &sh.full[s], k_col + c * 64, q_row, hq, b);
+                // the other operand: K rows of the key tile (dQ), Q / dO rows of the query tile (dK / dV)
+                const int b_row = i * kTile, b_head = KV ? hq : head / p.group;
+                for (int c = 0; c < hc; ++c)
+                    tma_load_4d(dst + (2 + c) * kChunkBytes, &maps.b, &sh.full[s], (half * hc + c) * 64, b_row, b_head,
+                                b);
+            }
+        }
+    } else if (warp == 4) {
+        if (lane == 0 && units > 0) {
+            const uint32_t idesc = umma_idesc(kTile, 64 * hc, BF16 ? 1 : 0, KV, true);
+            const uint32_t base = smem_u32(smem);
+            const uint64_t a_desc = KV ? umma_desc_sw128(base, kChunkBytes, 1024) : umma_desc_sw128(base, 16, 1024);
+            const uint64_t b_desc = umma_desc_sw128(base + 2 * kChunkBytes, kChunkBytes, 1024);
+            bool ok = true;
+            for (int u = 0; u < units && ok; ++u) {
+                const int s = u & 1;
+                ok = mbar_wait(&sh.full[s], (u >> 1) & 1, abort_word, 51);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk) {
+                    const uint32_t a_off = KV ? kk * 2048 : (kk / 4) * kChunkBytes + (kk % 4) * 32;
+                    umma_ss(tmem, umma_desc_advance(a_desc, s * stage_bytes + a_off),
+                            umma_desc_advance(b_desc, s * stage_bytes + kk * 2048), idesc, u > 0 || kk > 0);
+                }
+                umma_commit(&sh.empty[s]);
+            }
+            if (ok) umma_commit(&sh.done);
+        }
+    } else {
+        using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+        const int row = owner0 + warp * 32 + lane;
+        const int width = 64 * hc;
+        void* base = WHICH == 0 ? p.dq : WHICH == 1 ? p.dk : p.dv;
+        const int64_t* os = WHICH == 0 ? p.dqs : WHICH == 1 ? p.dks : p.dvs;
+        T* out = reinterpret_cast<T*>(base) + (int64_t)b * os[0] + (int64_t)head * os[1] + (int64_t)row * os[2] +
+                 half * width;
+        const float mul = WHICH == 2 ? 1.f : p.scale;
+        if (units == 0) {
+            if (row < owner_len)
+                for (int d = 0; d < width; d += 8) *reinterpret_cast<uint4*>(out + d) = make_uint4(0, 0, 0, 0);
+        } else if (mbar_wait(&sh.done, 0, abort_word, 52)) {
+            tc_fence_after();
+            const uint32_t acc = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+            for (int c = 0; c < width; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(acc + c, v);
+                tmem_wait_ld();
+                if (row < owner_len) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint4 o;
+                        o.x = pack2<BF16>(__uint_as_float(v[e]) * mul, __uint_as_float(v[e + 1]) * mul);
+                        o.y = pack2<BF16>(__uint_as_float(v[e + 2]) * mul, __uint_as_float(v[e + 3]) * mul);
+                        o.z = pack2<BF16>(__uint_as_float(v[e + 4]) * mul, __uint_as_float(v[e + 5]) * mul);
+                        o.w = pack2<BF16>(__uint_as_float(v[e + 6]) * mul, __uint_as_float(v[e + 7]) * mul);
+                        *reinterpret_cast<uint4*>(out + c + e) = o;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 3200 + sh.abort_word;
+    if (warp == 4) tmem_dealloc(tmem, 256);
+}
+
+// ------------------------------------------------------------------------------------ host side
+int smem_scores(int D) { return (D / 64 + kRing) * kChunkBytes + 1024 + 256; }
+int smem_grad(int D) { return 2 * (2 + D / 128) * kChunkBytes + 1024 + 256; }
+
+bool wide_common(const AttnParams& p) {
+    if (p.D != 256 && p.D != 384 && p.D != 512) return false;
+    if (p.nd != 0) return false;
+    if (p.scale == 0.f || p.Sk < 2) return false;  // exact-zero guarantees of those cases live in the general kernels
+    if (p.has_mask && p.ms[2] != 0) return false;  // only masks broadcast over the query axis
+    return tma_compatible(p.q, p.qs, p.B, p.Hq, p.Sq) && tma_compatible(p.k, p.ks, p.B, p.Hkv, p.Sk) &&
+           tma_compatible(p.v, p.vs, p.B, p.Hkv, p.Sk);
+}
+
+CUtensorMapDataType map_type(bool bf16) {
+    return bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+}
+
+bool encode_stored(CUtensorMap* map, const void* ptr, bool bf16, const AttnParams& p, int64_t pitch) {
+    const int64_t strides[4] = {(int64_t)p.Hq * p.Sq * pitch, (int64_t)p.Sq * pitch, pitch, 1};
+    return encode_bhsd_map(map, ptr, map_type(bf16), p.Sk, p.Sq, p.Hq, p.B, strides, 64, kTile);
+}
+
+template <typename K>
+cudaError_t opt_in(K kernel, int bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+template <bool BF16>
+cudaError_t forward_t(const AttnParams& p, cudaStream_t st) {
+    const int bytes = smem_scores(p.D);
+    cudaError_t e = opt_in(wide_forward<BF16>, bytes);
+    if (e != cudaSuccess) return e;
+    WideMaps maps;
+    const CUtensorMapDataType dt = map_type(BF16);
+    if (!encode_bhsd_map(&maps.a, p.q, dt, p.D, p.Sq, p.Hq, p.B, p.qs, 64, kTile) ||
+        !encode_bhsd_map(&maps.b, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kTile) ||
+        !encode_bhsd_map(&maps.c, p.v, dt, p.D, p.Sk, p.Hkv, p.B, p.vs, 64, kTile))
+        return cudaErrorInvalidValue;
+    const int64_t grid = (int64_t)((p.Sq + kTile - 1) / kTile) * p.B * p.Hq * 2;
+    wide_forward<BF16><<<(unsigned)grid, 256, bytes, st>>>(maps, p);
+    return cudaGetLastError();
+}
+
+template <int MODE, bool BF16>
+cudaError_t scores_t(const AttnParams& p, const Stored& stored, cudaStream_t st) {
+    const int bytes = smem_scores(p.D);
+    cudaError_t e = opt_in(wide_scores<MODE, BF16>, bytes);
+    if (e != cudaSuccess) return e;
+    WideMaps maps;
+    const CUtensorMapDataType dt = map_type(BF16);
+    const bool ok = MODE == 0 ? encode_bhsd_map(&maps.a, p.q, dt, p.D, p.Sq, p.Hq, p.B, p.qs, 64, kTile) &&
+                                    encode_bhsd_map(&maps.b, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kTile)
+                              : encode_bhsd_map(&maps.a, p.dout, dt, p.D, p.Sq, p.Hq, p.B, p.gs, 64, kTile) &&
+                                    encode_bhsd_map(&maps.b, p.v, dt, p.D, p.Sk, p.Hkv, p.B, p.vs, 64, kTile);
+    if (!ok) return cudaErrorInvalidValue;
+    maps.c = maps.a;
+    const int64_t grid = (int64_t)((p.Sq + kTile - 1) / kTile) * p.B * p.Hq;
+    wide_scores<MODE, BF16><<<(unsigned)grid, 256, bytes, st>>>(maps, p, stored);
+    return cudaGetLastError();
+}
+
+template <int WHICH, bool BF16>
+cudaError_t grad_t(const AttnParams& p, const Stored& stored, cudaStream_t st) {
+    const int bytes = smem_grad(p.D);
+    cudaError_t e = opt_in(wide_grad<WHICH, BF16>, bytes);
+    if (e != cudaSuccess) return e;
+    WideMaps maps;
+    const CUtensorMapDataType dt = map_type(BF16);
+    bool ok = encode_stored(&maps.a, WHICH == 2 ? stored.p_low : stored.ds_low, BF16, p, stored.pitch);
+    if (WHICH == 0) ok = ok && encode_bhsd_map(&maps.b, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kTile);
+    if (WHICH == 1) ok = ok && encode_bhsd_map(&maps.b, p.q, dt, p.D, p.Sq, p.Hq, p.B, p.qs, 64, kTile);
+    if (WHICH == 2) ok = ok && encode_bhsd_map(&maps.b, p.dout, dt, p.D, p.Sq, p.Hq, p.B, p.gs, 64, kTile);
+    if (!ok) return cudaErrorInvalidValue;
+    maps.c = maps.a;
+    const int owner_len = WHICH == 0 ? p.Sq : p.Sk, heads = WHICH == 0 ? p.Hq : p.Hkv;
+    const int64_t grid = (int64_t)((owner_len + kTile - 1) / kTile) * p.B * heads * 2;
+    wide_grad<WHICH, BF16><<<(unsigned)grid, 192, bytes, st>>>(maps, p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool wide_forward_supported(const AttnParams& p) {
+    return wide_common(p) && tma_compatible(p.out, p.os, p.B, p.Hq, p.Sq);
+}
+
+cudaError_t launch_wide_forward(const AttnParams& p, bool bf16, cudaStream_t st) {
+    return bf16 ? forward_t<true>(p, st) : forward_t<false>(p, st);
+}
+
+size_t wide_stored_bytes(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk) {
+    const int64_t pitch = (Sk + kTile - 1) / kTile * kTile;
+    return (size_t)((B * Hq * Sq * pitch * 2 + 255) / 256 * 256);
+}
+
+bool wide_backward_supported(const AttnParams& p) {
+    return wide_common(p) && tma_compatible(p.dout, p.gs, p.B, p.Hq, p.Sq) &&
+           tma_compatible(p.dq, p.dqs, p.B, p.Hq, p.Sq) && tma_compatible(p.dk, p.dks, p.B, p.Hkv, p.Sk) &&
+           tma_compatible(p.dv, p.dvs, p.B, p.Hkv, p.Sk);
+}
+
+// step 0: P_low, 1: dS_low, 2: dQ, 3: dK, 4: dV.  `stored` holds the two matrices back to back.
+cudaError_t launch_wide_backward(const AttnParams& p, bool bf16, int step, void* stored, cudaStream_t st) {
+    Stored s;
+    s.pitch = (p.Sk + kTile - 1) / kTile * kTile;
+    s.p_low = stored;
+    s.ds_low = static_cast<char*>(stored) + wide_stored_bytes(p.B, p.Hq, p.Sq, p.Sk);
+    switch (step) {
+        case 0: return bf16 ? scores_t<0, true>(p, s, st) : scores_t<0, false>(p, s, st);
+        case 1: return bf16 ? scores_t<1, true>(p, s, st) : scores_t<1, false>(p, s, st);
+        case 2: return bf16 ? grad_t<0, true>(p, s, st) : grad_t<0, false>(p, s, st);
+        case 3: return bf16 ? grad_t<1, true>(p, s, st) : grad_t<1, false>(p, s, st);
+        default: return bf16 ? grad_t<2, true>(p, s, st) : grad_t<2, false>(p, s, st);
+    }
+}
+
+}  // namespace kfa

@@ -74,6 +74,57 @@ def test_pipeline_shapes(shape, dtype):
     check_against_oracle(actual, q, k, v, dout, None, causal, None)
 
 
+WIDE_SHAPES = [
+    # B, Hq, Hkv, Sq, Sk, D, causal
+    (1, 1, 1, 128, 128, 256, False),
+    (1, 2, 1, 256, 256, 512, True),
+    (1, 2, 2, 65, 200, 256, False),
+    (1, 2, 1, 96, 96, 512, True),
+    (2, 4, 2, 129, 257, 384, False),
+    (1, 2, 2, 300, 300, 512, True),
+    (1, 2, 1, 1, 300, 256, False),
+    (1, 2, 2, 513, 140, 384, True),
+    (1, 2, 2, 140, 513, 512, True),
+    (1, 4, 1, 640, 640, 512, True),
+]
+
+
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
+@pytest.mark.parametrize("shape", WIDE_SHAPES)
+def test_wide_head_shapes(shape, dtype):
+    """Heads of 256/384/512 channels run on the tensor-memory kernels for wide heads (family 2)."""
+    B, Hq, Hkv, Sq, Sk, D, causal = shape
+    q, k, v, dout = make_inputs(B, Hq, Hkv, Sq, Sk, D, dtype, seed=hash(shape) % 1000)
+    assert native().selected_family(q, k, v, None, causal) == 2
+    assert native().selected_family(q, k, v, None, causal, backward=True) == 2
+    actual = run_attention(api().attention, q, k, v, dout, causal=causal)
+    check_against_oracle(actual, q, k, v, dout, None, causal, None)
+
+
+@pytest.mark.parametrize("scale", (-0.05, 0.2))
+@pytest.mark.parametrize("name", ("keys", "key_padding", "all_false"))
+def test_wide_head_masks_and_scales(name, scale):
+    B, Hq, Hkv, Sq, Sk, D = 2, 4, 2, 150, 330, 256
+    gen = torch.Generator().manual_seed(77)
+    mask = _mask_variants(B, Hq, Sq, Sk, gen)[name].cuda()
+    q, k, v, dout = make_inputs(B, Hq, Hkv, Sq, Sk, D, torch.bfloat16, seed=78)
+    actual = run_attention(api().attention, q, k, v, dout, mask=mask, causal=True, scale=scale)
+    check_against_oracle(actual, q, k, v, dout, mask, True, scale)
+    if name != "all_false":
+        hidden_keys = ~mask.expand(B, 1, 1, Sk)[:, 0, 0].cpu()
+        for grad in actual[2:]:
+            assert float(grad.cpu()[hidden_keys[:, None, :].expand(B, Hkv, Sk)].abs().max()) == 0
+
+
+def test_wide_head_projection_layout():
+    """[B, S, H, D] memory behind a [B, H, S, D] view is addressed through the tensor maps, no copy."""
+    q, k, v, dout = make_inputs(1, 4, 2, 200, 200, 512, torch.bfloat16, seed=79)
+    q, k, v = (strided_like_projection(t) for t in (q, k, v))
+    assert native().selected_family(q, k, v, None, True) == 2
+    actual = run_attention(api().attention, q, k, v, dout, causal=True)
+    check_against_oracle(actual, q, k, v, dout, None, True, None)
+
+
 GENERAL_SHAPES = [
     (1, 2, 1, 33, 49, 1, False),
     (1, 2, 2, 70, 65, 17, True),
