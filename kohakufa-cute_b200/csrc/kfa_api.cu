@@ -439,6 +439,7 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
     const bool pipeline = kfa::pipeline_backward_supported(p, bf16);
     const bool wide = !pipeline && kfa::wide_backward_supported(p) && wide_extra_bytes(q, k) > 0;
     cudaError_t ce = timed("output_delta", st, [&] {
+        if (wide) return kfa::launch_wide_delta(p, bf16, st);
         return pipeline ? kfa::launch_pipeline_delta(p, bf16, st) : kfa::launch_output_delta(p, bf16, st);
     });
     if (ce != cudaSuccess) return cuda_fail(ce, "output_delta launch");

@@ -32,6 +32,7 @@ bool wide_forward_supported(const AttnParams& p);
 cudaError_t launch_wide_forward(const AttnParams& p, bool bf16, cudaStream_t st);
 size_t wide_stored_bytes(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk);
 bool wide_backward_supported(const AttnParams& p);
+cudaError_t launch_wide_delta(const AttnParams& p, bool bf16, cudaStream_t st);
 cudaError_t launch_wide_backward(const AttnParams& p, bool bf16, int step, void* stored, cudaStream_t st);
 
 int pipeline_configured_variants();

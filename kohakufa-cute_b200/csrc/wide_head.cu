@@ -85,9 +85,12 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = blockIdx.x & 1;
     const int64_t rest = blockIdx.x >> 1;
+    // Tile-major block order: under a causal mask the late (heavy) query tiles of EVERY head are
+    // dispatched before any light one, which keeps the last wave short.
     const int nblk = (p.Sq + kTile - 1) / kTile;
-    const int qblk = nblk - 1 - (int)(rest % nblk);  // heavy (late) causal tiles first
-    const int64_t bh = rest / nblk;
+    const int64_t nbh = (int64_t)p.B * p.Hq;
+    const int qblk = nblk - 1 - (int)(rest / nbh);
+    const int64_t bh = rest % nbh;
     const int h = (int)(bh % p.Hq), b = (int)(bh / p.Hq);
     const int kvh = h / p.group;
     const int q0 = qblk * kTile;
@@ -154,10 +157,12 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
             int pos = 0, iter = 0;
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (key_tile_state(p, b, h, j) == 0) continue;
+                KFA_TRACE_POINT(0, 1);
                 for (int c = 0; c < chunks && ok; ++c, ++pos) {
                     const int slot = pos % kRing;
                     ok = mbar_wait(&sh.full[slot], (pos / kRing) & 1, abort_word, 21);
                     if (!ok) break;
+                    KFA_TRACE_POINT(0, 2);
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
@@ -170,8 +175,10 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
                 const int s0 = pos % kRing;
                 for (int i = 0; i < hc && ok; ++i)
                     ok = mbar_wait(&sh.full[(pos + i) % kRing], ((pos + i) / kRing) & 1, abort_word, 22);
+                KFA_TRACE_POINT(0, 3);
                 if (ok) ok = mbar_wait(&sh.p_ready, iter & 1, abort_word, 23);
                 if (!ok) break;
+                KFA_TRACE_POINT(0, 4);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk)
@@ -199,8 +206,10 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int state = key_tile_state(p, b, h, j);
             if (state == 0) continue;
+            KFA_TRACE_POINT(1, 1);
             ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 30);
             if (!ok) break;
+            KFA_TRACE_POINT(1, 2);
             tc_fence_after();
             float s[kTile];
 #pragma unroll
@@ -282,6 +291,7 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&sh.p_ready);
+            KFA_TRACE_POINT(1, 3);
             ++iter;
         }
         T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] + (int64_t)row * p.os[2] +
@@ -335,6 +345,7 @@ struct Stored {
     void* p_low;
     void* ds_low;
     int64_t pitch;
+    int parts;  // CTAs that share one query tile's key tiles (tile j goes to part j % parts)
 };
 
 struct ScoreShared {
@@ -362,8 +373,11 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nblk = (p.Sq + kTile - 1) / kTile;
-    const int qblk = nblk - 1 - (int)(blockIdx.x % nblk);
-    const int64_t bh = blockIdx.x / nblk;
+    const int64_t nbh = (int64_t)p.B * p.Hq;
+    const int part = (int)(blockIdx.x % st.parts);
+    const int64_t rest = blockIdx.x / st.parts;
+    const int qblk = nblk - 1 - (int)(rest / nbh);  // tile-major order, heavy causal tiles first
+    const int64_t bh = rest % nbh;
     const int h = (int)(bh % p.Hq), b = (int)(bh / p.Hq);
     const int kvh = h / p.group;
     const int q0 = qblk * kTile;
@@ -401,7 +415,7 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
                 tma_load_4d(sOwn + c * kChunkBytes, &maps.a, &sh.own_full, c * 64, q0, h, b);
             int pos = 0;
             bool ok = true;
-            for (int j = 0; j < n_tiles && ok; ++j)
+            for (int j = part; j < n_tiles && ok; j += st.parts)
                 for (int c = 0; c < chunks && ok; ++c, ++pos) {
                     const int slot = pos % kRing, round = pos / kRing;
                     if (round > 0) ok = mbar_wait(&sh.empty[slot], (round - 1) & 1, abort_word, 40);
@@ -418,9 +432,9 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
             const uint64_t b_desc = umma_desc_sw128(smem_u32(sRing), 16, 1024);
             bool ok = mbar_wait(&sh.own_full, 0, abort_word, 41);
             int pos = 0;
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int buf = j & 1;
-                if (j >= 2) ok = mbar_wait(&sh.s_free[buf], ((j >> 1) - 1) & 1, abort_word, 42);
+            for (int n = 0; part + n * st.parts < n_tiles && ok; ++n) {
+                const int buf = n & 1;
+                if (n >= 2) ok = mbar_wait(&sh.s_free[buf], ((n >> 1) - 1) & 1, abort_word, 42);
                 if (!ok) break;
                 tc_fence_after();
                 for (int c = 0; c < chunks && ok; ++c, ++pos) {
@@ -459,14 +473,15 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
         uint16_t* p_row = reinterpret_cast<uint16_t*>(st.p_low) + row_off;
         uint16_t* ds_row = reinterpret_cast<uint16_t*>(st.ds_low) + row_off;
         bool ok = true;
-        for (int j = 0; j < n_tiles && ok; ++j) {
-            const int buf = j & 1, key0 = j * kTile;
+        for (int n = 0; part + n * st.parts < n_tiles && ok; ++n) {
+            const int j = part + n * st.parts;
+            const int buf = n & 1, key0 = j * kTile;
             uint4 pl[16];
             if (MODE == 1 && row_ok) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) pl[i] = *reinterpret_cast<const uint4*>(p_row + key0 + i * 8);
             }
-            ok = mbar_wait(&sh.s_ready[buf], (j >> 1) & 1, abort_word, 44);
+            ok = mbar_wait(&sh.s_ready[buf], (n >> 1) & 1, abort_word, 44);
             if (!ok) break;
             tc_fence_after();
             float s[kTile];
@@ -563,9 +578,10 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Wide
     const int64_t rest = blockIdx.x >> 1;
     const int owner_len = KV ? p.Sk : p.Sq, heads = KV ? p.Hkv : p.Hq;
     const int nblk = (owner_len + kTile - 1) / kTile;
-    int blk = (int)(rest % nblk);
+    const int64_t nbh = (int64_t)p.B * heads;
+    int blk = (int)(rest / nbh);    // tile-major order over all heads
     if (!KV) blk = nblk - 1 - blk;  // causal: late query tiles and early key tiles carry the most work
-    const int64_t bh = rest / nblk;
+    const int64_t bh = rest % nbh;
     const int head = (int)(bh % heads), b = (int)(bh / heads);
     const int owner0 = blk * kTile;
     // streamed tile range and the number of passes over it (query heads of the group)
@@ -683,6 +699,30 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Wide
     if (warp == 4) tmem_dealloc(tmem, 256);
 }
 
+// delta[row] = sum_d f32(O) f32(dO): one warp per row, 16-byte loads.
+template <typename T>
+__global__ void __launch_bounds__(256) wide_delta(AttnParams p) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row_id = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
+    if (row_id >= rows) return;
+    const int r = (int)(row_id % p.Sq);
+    const int h = (int)((row_id / p.Sq) % p.Hq);
+    const int b = (int)(row_id / ((int64_t)p.Sq * p.Hq));
+    const T* o = reinterpret_cast<const T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] + (int64_t)r * p.os[2];
+    const T* g = reinterpret_cast<const T*>(p.dout) + (int64_t)b * p.gs[0] + (int64_t)h * p.gs[1] + (int64_t)r * p.gs[2];
+    float sum = 0.f;
+    for (int d = lane * 8; d < p.D; d += 256) {
+        const uint4 ov = *reinterpret_cast<const uint4*>(o + d), gv = *reinterpret_cast<const uint4*>(g + d);
+        const T* oe = reinterpret_cast<const T*>(&ov);
+        const T* ge = reinterpret_cast<const T*>(&gv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum = fmaf(to_float<T>(oe[e]), to_float<T>(ge[e]), sum);
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) p.delta[row_id] = sum;
+}
+
 // ------------------------------------------------------------------------------------ host side
 int smem_scores(int D) { return (D / 64 + kRing) * kChunkBytes + 1024 + 256; }
 int smem_grad(int D) { return 2 * (2 + D / 128) * kChunkBytes + 1024 + 256; }
@@ -739,7 +779,7 @@ cudaError_t scores_t(const AttnParams& p, const Stored& stored, cudaStream_t st)
                                     encode_bhsd_map(&maps.b, p.v, dt, p.D, p.Sk, p.Hkv, p.B, p.vs, 64, kTile);
     if (!ok) return cudaErrorInvalidValue;
     maps.c = maps.a;
-    const int64_t grid = (int64_t)((p.Sq + kTile - 1) / kTile) * p.B * p.Hq;
+    const int64_t grid = (int64_t)((p.Sq + kTile - 1) / kTile) * p.B * p.Hq * stored.parts;
     wide_scores<MODE, BF16><<<(unsigned)grid, 256, bytes, st>>>(maps, p, stored);
     return cudaGetLastError();
 }
@@ -780,14 +820,24 @@ size_t wide_stored_bytes(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk) {
 
 bool wide_backward_supported(const AttnParams& p) {
     return wide_common(p) && tma_compatible(p.dout, p.gs, p.B, p.Hq, p.Sq) &&
+           tma_compatible(p.out, p.os, p.B, p.Hq, p.Sq) &&
            tma_compatible(p.dq, p.dqs, p.B, p.Hq, p.Sq) && tma_compatible(p.dk, p.dks, p.B, p.Hkv, p.Sk) &&
            tma_compatible(p.dv, p.dvs, p.B, p.Hkv, p.Sk);
+}
+
+cudaError_t launch_wide_delta(const AttnParams& p, bool bf16, cudaStream_t st) {
+    const unsigned grid = (unsigned)(((int64_t)p.B * p.Hq * p.Sq + 7) / 8);
+    if (bf16) wide_delta<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+    else wide_delta<__half><<<grid, 256, 0, st>>>(p);
+    return cudaGetLastError();
 }
 
 // step 0: P_low, 1: dS_low, 2: dQ, 3: dK, 4: dV.  `stored` holds the two matrices back to back.
 cudaError_t launch_wide_backward(const AttnParams& p, bool bf16, int step, void* stored, cudaStream_t st) {
     Stored s;
     s.pitch = (p.Sk + kTile - 1) / kTile * kTile;
+    // few query tiles: two CTAs share each tile's key range so that the grid covers the GPU
+    s.parts = (int64_t)((p.Sq + kTile - 1) / kTile) * p.B * p.Hq < 600 && p.Sk > kTile ? 2 : 1;
     s.p_low = stored;
     s.ds_low = static_cast<char*>(stored) + wide_stored_bytes(p.B, p.Hq, p.Sq, p.Sk);
     switch (step) {
@@ -798,5 +848,16 @@ cudaError_t launch_wide_backward(const AttnParams& p, bool bf16, int step, void*
         default: return bf16 ? grad_t<2, true>(p, s, st) : grad_t<2, false>(p, s, st);
     }
 }
+
+#ifdef KFA_TRACE
+extern "C" __attribute__((visibility("default"))) int kfa_debug_trace_wide(long long* out, int* counts) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_kfa_trace, sizeof(long long) * 4 * 1024);
+    cudaMemcpyFromSymbol(counts, g_kfa_trace_n, sizeof(int) * 4);
+    int zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_kfa_trace_n, zero, sizeof(zero));
+    return 0;
+}
+#endif
 
 }  // namespace kfa
