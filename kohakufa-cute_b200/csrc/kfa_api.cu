@@ -507,8 +507,11 @@ int kfa_neighborhood_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa
     p.logsum = static_cast<float*>(logsum->data);
     p.two_term = nd == 3 ? 1 : 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    cudaError_t ce = timed("neighborhood_forward", st,
-                           [&] { return kfa::launch_neighborhood_forward(p, q->dtype == KFA_BF16, st); });
+    const bool bf16 = q->dtype == KFA_BF16;
+    cudaError_t ce = kfa::na_pipeline_forward_supported(p)
+                         ? timed("na_pipeline_forward", st, [&] { return kfa::launch_na_pipeline_forward(p, bf16, st); })
+                         : timed("neighborhood_forward", st,
+                                 [&] { return kfa::launch_neighborhood_forward(p, bf16, st); });
     if (ce != cudaSuccess) return cuda_fail(ce, "neighborhood forward launch");
     return 0;
 }

@@ -35,6 +35,10 @@ bool wide_backward_supported(const AttnParams& p);
 cudaError_t launch_wide_delta(const AttnParams& p, bool bf16, cudaStream_t st);
 cudaError_t launch_wide_backward(const AttnParams& p, bool bf16, int step, void* stored, cudaStream_t st);
 
+// Neighbourhood attention on the tensor-memory pipeline (dense tiles + per-row window bit masks).
+bool na_pipeline_forward_supported(const AttnParams& p);
+cudaError_t launch_na_pipeline_forward(const AttnParams& p, bool bf16, cudaStream_t st);
+
 int pipeline_configured_variants();
 void pipeline_forget_variants();
 

@@ -1,0 +1,92 @@
+// Neighbourhood attention on dense tensor-core tiles: window geometry as tile lists and bit masks.
+//
+// Tokens are numbered z-major, x fastest.  A query sees the box of keys
+// [z0, z0+wz) x [y0, y0+wy) x [x0, x0+wx) with starts clamp(q - w/2, 0, extent - w); a key is seen
+// by the box of queries given by the inverse ranges (reference behaviour:
+// src/kohakufa_cute/neighborhood_kernels.py:193-212 of the reference project).  Either way the
+// visible partners of one token are a box, and inside one (z, y) row of the grid a box is a
+// contiguous run of tokens.  The kernels therefore
+//   * mark, per CTA, the dense tiles of partner tokens that any of their 128 owner rows can see
+//     (a bitmap in shared memory, built once), and walk only those tiles;
+//   * give every owner row a bit mask per tile (one bit per partner token) that is applied to the
+//     dense score tile, so that exactly the window contributes.
+#pragma once
+#include "kfa_common.cuh"
+
+namespace kfa {
+namespace na {
+
+constexpr int kMapWords = 128;  // up to 4096 tiles per partner sequence
+
+struct Box {
+    int zlo, zhi, ylo, yhi, xlo, xhi;  // inclusive coordinate ranges
+};
+
+// Keys visible to query `token`.
+__device__ __forceinline__ Box query_box(const AttnParams& p, int token) {
+    const int x = token % p.ext[2], t = token / p.ext[2], y = t % p.ext[1], z = t / p.ext[1];
+    Box b;
+    b.zlo = na_start(z, p.ext[0], p.win[0]);
+    b.zhi = b.zlo + p.win[0] - 1;
+    b.ylo = na_start(y, p.ext[1], p.win[1]);
+    b.yhi = b.ylo + p.win[1] - 1;
+    b.xlo = na_start(x, p.ext[2], p.win[2]);
+    b.xhi = b.xlo + p.win[2] - 1;
+    return b;
+}
+
+// Queries that see key `token`.
+__device__ __forceinline__ Box key_box(const AttnParams& p, int token) {
+    const int x = token % p.ext[2], t = token / p.ext[2], y = t % p.ext[1], z = t / p.ext[1];
+    Box b;
+    na_inverse(z, p.ext[0], p.win[0], b.zlo, b.zhi);
+    na_inverse(y, p.ext[1], p.win[1], b.ylo, b.yhi);
+    na_inverse(x, p.ext[2], p.win[2], b.xlo, b.xhi);
+    return b;
+}
+
+// Sets, in the shared bitmap, every tile of `width` partner tokens that the box touches.
+__device__ __forceinline__ void mark_tiles(const AttnParams& p, const Box& b, int width, uint32_t* bitmap) {
+    for (int z = b.zlo; z <= b.zhi; ++z)
+        for (int y = b.ylo; y <= b.yhi; ++y) {
+            const int row0 = (z * p.ext[1] + y) * p.ext[2];
+            const int first = (row0 + b.xlo) / width, last = (row0 + b.xhi) / width;
+            for (int t = first; t <= last; ++t) atomicOr(&bitmap[t >> 5], 1u << (t & 31));
+        }
+}
+
+// First marked tile with index >= j, or -1.
+__device__ __forceinline__ int next_tile(const uint32_t* bitmap, int j) {
+    int w = j >> 5;
+    if (w >= kMapWords) return -1;
+    uint32_t cur = bitmap[w] & (0xffffffffu << (j & 31));
+    while (cur == 0) {
+        if (++w >= kMapWords) return -1;
+        cur = bitmap[w];
+    }
+    return (w << 5) + __ffs(cur) - 1;
+}
+
+// Bit c of the result (word c / 32) is set when partner token tok0 + c lies in the box.
+// `limit` is the length of the partner sequence.
+template <int WORDS>
+__device__ __forceinline__ void box_mask(const AttnParams& p, const Box& b, int tok0, int limit, uint32_t (&m)[WORDS]) {
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) m[w] = 0;
+    const int ex = p.ext[2], ey = p.ext[1];
+    const int r_first = tok0 / ex, r_last = (min(tok0 + 32 * WORDS, limit) - 1) / ex;
+    for (int r = r_first; r <= r_last; ++r) {
+        const int z = r / ey, y = r - z * ey;
+        if (z < b.zlo || z > b.zhi || y < b.ylo || y > b.yhi) continue;
+        const int lo = max(r * ex + b.xlo - tok0, 0), hi = min(r * ex + b.xhi - tok0, 32 * WORDS - 1);
+        if (lo > hi) continue;
+#pragma unroll
+        for (int w = 0; w < WORDS; ++w) {
+            const int a = max(lo - 32 * w, 0), e = min(hi - 32 * w, 31);
+            if (a <= e) m[w] |= static_cast<uint32_t>(((1ull << (e - a + 1)) - 1ull) << a);
+        }
+    }
+}
+
+}  // namespace na
+}  // namespace kfa
