@@ -556,8 +556,18 @@ int kfa_neighborhood_backward(const kfa_tensor* q, const kfa_tensor* k, const kf
     copy4(p.dvs, dv->strides);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool bf16 = q->dtype == KFA_BF16;
-    cudaError_t ce = timed("output_delta", st, [&] { return kfa::launch_output_delta(p, bf16, st); });
+    const bool tensor_path = kfa::na_pipeline_backward_supported(p);
+    cudaError_t ce = timed("output_delta", st, [&] {
+        return tensor_path ? kfa::launch_pipeline_delta(p, bf16, st) : kfa::launch_output_delta(p, bf16, st);
+    });
     if (ce != cudaSuccess) return cuda_fail(ce, "output_delta launch");
+    if (tensor_path) {
+        ce = timed("na_pipeline_backward_q", st, [&] { return kfa::launch_na_pipeline_backward(p, bf16, 0, st); });
+        if (ce != cudaSuccess) return cuda_fail(ce, "neighborhood pipeline backward (dQ) launch");
+        ce = timed("na_pipeline_backward_kv", st, [&] { return kfa::launch_na_pipeline_backward(p, bf16, 1, st); });
+        if (ce != cudaSuccess) return cuda_fail(ce, "neighborhood pipeline backward (dK/dV) launch");
+        return 0;
+    }
     ce = timed("neighborhood_backward_q", st, [&] { return kfa::launch_neighborhood_backward(p, bf16, 0, st); });
     if (ce != cudaSuccess) return cuda_fail(ce, "neighborhood backward (dQ) launch");
     ce = timed("neighborhood_backward_kv", st, [&] { return kfa::launch_neighborhood_backward(p, bf16, 1, st); });

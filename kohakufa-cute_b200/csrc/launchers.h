@@ -38,6 +38,8 @@ cudaError_t launch_wide_backward(const AttnParams& p, bool bf16, int step, void*
 // Neighbourhood attention on the tensor-memory pipeline (dense tiles + per-row window bit masks).
 bool na_pipeline_forward_supported(const AttnParams& p);
 cudaError_t launch_na_pipeline_forward(const AttnParams& p, bool bf16, cudaStream_t st);
+bool na_pipeline_backward_supported(const AttnParams& p);
+cudaError_t launch_na_pipeline_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st);
 
 int pipeline_configured_variants();
 void pipeline_forget_variants();

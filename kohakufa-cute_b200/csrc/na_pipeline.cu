@@ -274,6 +274,287 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
     if (warp == 4) tmem_dealloc(tmem, 256);
 }
 
+// ----------------------------------------------------------------------------------------- backward
+constexpr int kSub = 64;                      // partner tokens per streamed tile
+constexpr int kSubBytes = kSub * 128;         // 64 rows x 64 channels
+constexpr int kStages = 4;                    // ring stages, each holds both streamed operands
+
+struct BwdShared {
+    uint64_t own_full;
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t sdp_ready;
+    uint64_t ops_ready;
+    uint64_t done;
+    uint32_t tmem_base;
+    int abort_word;
+    uint32_t bitmap[kMapWords];
+    float stats[2][4][kSub];  // per streamed query: maximum, logsum, delta, t (key owners only)
+};
+
+struct BwdMaps {
+    CUtensorMap own0, own1, st0, st1;
+};
+
+// KV = false: the CTA owns 128 queries (own0 = Q, own1 = dO) and streams (K, V) tiles of 64 keys.
+// KV = true:  the CTA owns 128 keys (own0 = K, own1 = V) and streams (Q, dO) tiles of 64 queries.
+// Per streamed tile the tensor core forms S and dP (owner rows x 64), the consumer warps turn them
+// into two 16-bit operands in place, and two accumulators collect
+//   KV = false:  acc0 += dS_q K,       acc1 += rd(P32) K
+//   KV = true:   acc0 += rd(P32)^T dO,  acc1 += dS_k^T Q
+// Tensor memory (256 columns): S at 0, dP at 64, acc0 at 128, acc1 at 192.
+template <bool KV, bool BF16>
+__global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__ BwdMaps maps, AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sOwn = smem;                         // two owner operands, 16 KB each
+    uint8_t* sRing = smem + 2 * kChunkBytes;      // stages of (streamed 0, streamed 1), 8 KB each
+    BwdShared& sh = *reinterpret_cast<BwdShared*>(sRing + kStages * 2 * kSubBytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int owner_len = KV ? p.Sk : p.Sq, partner_len = KV ? p.Sq : p.Sk;
+    const int nblk = (owner_len + kTile - 1) / kTile;
+    const int blk = (int)(blockIdx.x % nblk);
+    const int64_t bh = blockIdx.x / nblk;
+    const int h = (int)(bh % p.Hq), b = (int)(bh / p.Hq);
+    const int owner0 = blk * kTile;
+
+    if (threadIdx.x == 0) {
+        sh.abort_word = 0;
+        mbar_init(&sh.own_full, 1);
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&sh.full[i], 1);
+            mbar_init(&sh.empty[i], 1);
+        }
+        mbar_init(&sh.sdp_ready, 1);
+        mbar_init(&sh.ops_ready, kTile);
+        mbar_init(&sh.done, 1);
+        mbar_fence_init();
+    }
+    for (int i = threadIdx.x; i < kMapWords; i += blockDim.x) sh.bitmap[i] = 0;
+    if (warp == 4) {
+        tmem_alloc(&sh.tmem_base, 256);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const int row = owner0 + warp * 32 + lane;
+    const bool row_ok = warp < 4 && row < owner_len;
+    Box box = {0, -1, 0, -1, 0, -1};
+    if (row_ok) {
+        box = KV ? key_box(p, row) : query_box(p, row);
+        mark_tiles(p, box, kSub, sh.bitmap);
+    }
+    __syncthreads();
+    const uint32_t tmem = sh.tmem_base;
+    volatile int* abort_word = &sh.abort_word;
+
+    if (warp == 5) {
+        if (lane == 0) {
+            tma_prefetch_desc(&maps.own0);
+            tma_prefetch_desc(&maps.own1);
+            tma_prefetch_desc(&maps.st0);
+            tma_prefetch_desc(&maps.st1);
+            mbar_expect_tx(&sh.own_full, 2 * kChunkBytes);
+            tma_load_4d(sOwn, &maps.own0, &sh.own_full, 0, owner0, h, b);
+            tma_load_4d(sOwn + kChunkBytes, &maps.own1, &sh.own_full, 0, owner0, h, b);
+            int n = 0;
+            bool ok = true;
+            for (int j = next_tile(sh.bitmap, 0); j >= 0 && ok; j = next_tile(sh.bitmap, j + 1), ++n) {
+                const int st = n % kStages, round = n / kStages;
+                if (round > 0) ok = mbar_wait(&sh.empty[st], (round - 1) & 1, abort_word, 60);
+                if (!ok) break;
+                mbar_expect_tx(&sh.full[st], 2 * kSubBytes);
+                tma_load_4d(sRing + st * 2 * kSubBytes, &maps.st0, &sh.full[st], 0, j * kSub, h, b);
+                tma_load_4d(sRing + st * 2 * kSubBytes + kSubBytes, &maps.st1, &sh.full[st], 0, j * kSub, h, b);
+            }
+        }
+    } else if (warp == 4) {
+        if (lane == 0) {
+            const uint32_t idesc_s = umma_idesc(kTile, kSub, BF16 ? 1 : 0, false, false);
+            const uint32_t idesc_neg = idesc_s | (p.scale < 0.f ? kUmmaNegateA : 0u);
+            constexpr uint32_t idesc_g = umma_idesc(kTile, 64, BF16 ? 1 : 0, false, true);
+            const uint64_t own_desc = umma_desc_sw128(smem_u32(sOwn), 16, 1024);
+            const uint64_t ring_k = umma_desc_sw128(smem_u32(sRing), 16, 1024);          // K-major view (scores)
+            const uint64_t ring_mn = umma_desc_sw128(smem_u32(sRing), kSubBytes, 1024);  // MN-major view (gradients)
+            bool ok = mbar_wait(&sh.own_full, 0, abort_word, 61);
+            int n = 0;
+            for (int j = next_tile(sh.bitmap, 0); j >= 0 && ok; j = next_tile(sh.bitmap, j + 1), ++n) {
+                const int st = n % kStages;
+                const uint32_t base = st * 2 * kSubBytes;
+                ok = mbar_wait(&sh.full[st], (n / kStages) & 1, abort_word, 62);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    umma_ss(tmem, umma_desc_advance(own_desc, kk * 32), umma_desc_advance(ring_k, base + kk * 32),
+                            idesc_neg, kk > 0);
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    umma_ss(tmem + 64, umma_desc_advance(own_desc, kChunkBytes + kk * 32),
+                            umma_desc_advance(ring_k, base + kSubBytes + kk * 32), idesc_s, kk > 0);
+                umma_commit(&sh.sdp_ready);
+                ok = mbar_wait(&sh.ops_ready, n & 1, abort_word, 63);
+                if (!ok) break;
+                tc_fence_after();
+                // acc0: operand over S with streamed K (query owners) / dO (key owners)
+                const uint32_t b0 = base + (KV ? kSubBytes : 0);
+#pragma unroll
+                for (int kk = 0; kk < kSub / 16; ++kk)
+                    umma_ts(tmem + 128, tmem + kk * 8, umma_desc_advance(ring_mn, b0 + kk * 2048), idesc_g,
+                            n > 0 || kk > 0);
+                // acc1: operand over dP with streamed K (query owners) / Q (key owners)
+#pragma unroll
+                for (int kk = 0; kk < kSub / 16; ++kk)
+                    umma_ts(tmem + 192, tmem + 64 + kk * 8, umma_desc_advance(ring_mn, base + kk * 2048), idesc_g,
+                            n > 0 || kk > 0);
+                umma_commit(&sh.empty[st]);
+            }
+            if (ok) umma_commit(&sh.done);
+        }
+    } else {
+        using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        const float c2 = fabsf(p.scale) * kLog2e;
+        const int64_t stat0 = ((int64_t)b * p.Hq + h) * p.Sq;
+        float row_m = INFINITY, row_ls = 0.f, row_dl = 0.f;
+        if (!KV && row_ok) {
+            row_m = p.maximum[stat0 + row];
+            row_ls = p.logsum[stat0 + row];
+            row_dl = p.delta[stat0 + row];
+            if (row_m == -INFINITY) row_m = INFINITY;
+        }
+        float sum_ds = 0.f, mass = 0.f, t_num = 0.f, t_den = 0.f;
+        const int tid = warp * 32 + lane;
+        int n = 0;
+        bool ok = true;
+        for (int j = next_tile(sh.bitmap, 0); j >= 0 && ok; j = next_tile(sh.bitmap, j + 1), ++n) {
+            const int part0 = j * kSub;
+            if (KV) {
+                // stage the statistics of the 64 streamed queries (two threads per query)
+                float* stat = &sh.stats[n & 1][0][0];
+                if (tid < kSub) {
+                    const int qi = part0 + tid;
+                    const bool in = qi < p.Sq;
+                    float m = in ? p.maximum[stat0 + qi] : INFINITY;
+                    if (m == -INFINITY) m = INFINITY;
+                    stat[tid] = m;
+                    stat[kSub + tid] = in ? p.logsum[stat0 + qi] : 0.f;
+                } else {
+                    const int qi = part0 + tid - kSub;
+                    const bool in = qi < p.Sq;
+                    stat[2 * kSub + tid - kSub] = in ? p.delta[stat0 + qi] : 0.f;
+                    stat[3 * kSub + tid - kSub] = in ? p.aux[stat0 + qi] : 0.f;
+                }
+                bar_sync(1, kTile);
+            }
+            uint32_t vis[2] = {0, 0};
+            if (row_ok) box_mask<2>(p, box, part0, partner_len, vis);
+            ok = mbar_wait(&sh.sdp_ready, n & 1, abort_word, 64);
+            if (!ok) break;
+            tc_fence_after();
+            const float* stat = &sh.stats[n & 1][0][0];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t s[32], dp[32], w0[16], w1[16];
+                tmem_ld32(lane_base + half * 32, s);
+                tmem_ld32(lane_base + 64 + half * 32, dp);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    float m = row_m, ls = row_ls, dl = row_dl, tt = 0.f;
+                    if (KV) {
+                        m = stat[half * 32 + c];
+                        ls = stat[kSub + half * 32 + c];
+                        dl = stat[2 * kSub + half * 32 + c];
+                        tt = stat[3 * kSub + half * 32 + c];
+                    }
+                    float p32 = ex2((__uint_as_float(s[c]) - m) * c2 - ls);
+                    p32 = (vis[half] >> c) & 1u ? p32 : 0.f;
+                    const float res = __uint_as_float(dp[c]) - dl;
+                    const float pl = round_low<T>(p32);
+                    // a hidden entry contributes an exact zero whatever dP holds
+                    const float prod = p32 == 0.f ? 0.f : p32 * (KV ? res - tt : res);
+                    const float ds = round_low<T>(prod);
+                    if (!KV) {
+                        sum_ds += ds;
+                        mass += pl;
+                        t_num += prod;
+                        t_den += p32;
+                    }
+                    // 16-bit operands: over S goes dS_q (query owners) / rd(P32) (key owners); over dP the other
+                    const float over_s = KV ? pl : ds, over_dp = KV ? ds : pl;
+                    s[c] = __float_as_uint(over_s);
+                    dp[c] = __float_as_uint(over_dp);
+                }
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    w0[c / 2] = pack2<BF16>(__uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+                    w1[c / 2] = pack2<BF16>(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1]));
+                }
+                tmem_st16(lane_base + half * 16, w0);
+                tmem_st16(lane_base + 64 + half * 16, w1);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sh.ops_ready);
+        }
+        if (n > 0 && ok) ok = mbar_wait(&sh.done, 0, abort_word, 65);
+        if (ok) {
+            tc_fence_after();
+            T* out0 = nullptr;
+            T* out1 = nullptr;
+            const int r = row_ok ? row : 0;
+            if (KV) {
+                out0 = reinterpret_cast<T*>(p.dv) + (int64_t)b * p.dvs[0] + (int64_t)h * p.dvs[1] + (int64_t)r * p.dvs[2];
+                out1 = reinterpret_cast<T*>(p.dk) + (int64_t)b * p.dks[0] + (int64_t)h * p.dks[1] + (int64_t)r * p.dks[2];
+            } else {
+                out0 = reinterpret_cast<T*>(p.dq) + (int64_t)b * p.dqs[0] + (int64_t)h * p.dqs[1] + (int64_t)r * p.dqs[2];
+            }
+            const float ratio = mass != 0.f ? sum_ds / mass : 0.f;
+#pragma unroll
+            for (int c = 0; c < 64; c += 32) {
+                uint32_t a0[32], a1[32];
+                if (n > 0) {
+                    tmem_ld32(lane_base + 128 + c, a0);
+                    tmem_ld32(lane_base + 192 + c, a1);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) a0[i] = a1[i] = 0;
+                }
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        float x[8], y[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float u = __uint_as_float(a0[i + e]), v = __uint_as_float(a1[i + e]);
+                            x[e] = KV ? u : (u - ratio * v) * p.scale;
+                            y[e] = v * p.scale;
+                        }
+                        *reinterpret_cast<uint4*>(out0 + c + i) =
+                            make_uint4(pack2<BF16>(x[0], x[1]), pack2<BF16>(x[2], x[3]), pack2<BF16>(x[4], x[5]),
+                                       pack2<BF16>(x[6], x[7]));
+                        if (KV)
+                            *reinterpret_cast<uint4*>(out1 + c + i) =
+                                make_uint4(pack2<BF16>(y[0], y[1]), pack2<BF16>(y[2], y[3]), pack2<BF16>(y[4], y[5]),
+                                           pack2<BF16>(y[6], y[7]));
+                    }
+                }
+            }
+            if (!KV && row_ok) p.aux[stat0 + row] = t_den != 0.f ? t_num / t_den : 0.f;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 4100 + sh.abort_word;
+    if (warp == 4) tmem_dealloc(tmem, 256);
+}
+
+constexpr int kBwdSmem = 2 * kChunkBytes + kStages * 2 * kSubBytes + 4096 + 1024;
+
 constexpr int kFwdSmem = (1 + kRing) * kChunkBytes + 1024 + 1024;
 
 bool encode_all(NaMaps* maps, const AttnParams& p, bool bf16, bool backward, int box_rows_partner) {
@@ -301,6 +582,32 @@ cudaError_t forward_t(const AttnParams& p, cudaStream_t st) {
     return cudaGetLastError();
 }
 
+template <bool KV, bool BF16>
+cudaError_t backward_t(const AttnParams& p, cudaStream_t st) {
+    cudaError_t e =
+        cudaFuncSetAttribute(na_tc_backward<KV, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
+    if (e != cudaSuccess) return e;
+    const CUtensorMapDataType dt = BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    BwdMaps maps;
+    bool ok;
+    if (KV) {
+        ok = encode_bhsd_map(&maps.own0, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kTile) &&
+             encode_bhsd_map(&maps.own1, p.v, dt, p.D, p.Sk, p.Hkv, p.B, p.vs, 64, kTile) &&
+             encode_bhsd_map(&maps.st0, p.q, dt, p.D, p.Sq, p.Hq, p.B, p.qs, 64, kSub) &&
+             encode_bhsd_map(&maps.st1, p.dout, dt, p.D, p.Sq, p.Hq, p.B, p.gs, 64, kSub);
+    } else {
+        ok = encode_bhsd_map(&maps.own0, p.q, dt, p.D, p.Sq, p.Hq, p.B, p.qs, 64, kTile) &&
+             encode_bhsd_map(&maps.own1, p.dout, dt, p.D, p.Sq, p.Hq, p.B, p.gs, 64, kTile) &&
+             encode_bhsd_map(&maps.st0, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kSub) &&
+             encode_bhsd_map(&maps.st1, p.v, dt, p.D, p.Sk, p.Hkv, p.B, p.vs, 64, kSub);
+    }
+    if (!ok) return cudaErrorInvalidValue;
+    const int owner_len = KV ? p.Sk : p.Sq;
+    const int64_t grid = (int64_t)((owner_len + kTile - 1) / kTile) * p.B * p.Hq;
+    na_tc_backward<KV, BF16><<<(unsigned)grid, 192, kBwdSmem, st>>>(maps, p);
+    return cudaGetLastError();
+}
+
 bool common_supported(const AttnParams& p) {
     if (p.nd != 2 && p.nd != 3) return false;
     if (p.D != 64 || p.Hq != p.Hkv || p.Sq != p.Sk) return false;
@@ -318,6 +625,18 @@ bool na_pipeline_forward_supported(const AttnParams& p) {
 
 cudaError_t launch_na_pipeline_forward(const AttnParams& p, bool bf16, cudaStream_t st) {
     return bf16 ? forward_t<true>(p, st) : forward_t<false>(p, st);
+}
+
+bool na_pipeline_backward_supported(const AttnParams& p) {
+    return common_supported(p) && tma_compatible(p.out, p.os, p.B, p.Hq, p.Sq) &&
+           tma_compatible(p.dout, p.gs, p.B, p.Hq, p.Sq) && tma_compatible(p.dq, p.dqs, p.B, p.Hq, p.Sq) &&
+           tma_compatible(p.dk, p.dks, p.B, p.Hkv, p.Sk) && tma_compatible(p.dv, p.dvs, p.B, p.Hkv, p.Sk);
+}
+
+// which 0: dQ and the per-query correction t (must run first); 1: dK and dV.
+cudaError_t launch_na_pipeline_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st) {
+    if (which == 0) return bf16 ? backward_t<false, true>(p, st) : backward_t<false, false>(p, st);
+    return bf16 ? backward_t<true, true>(p, st) : backward_t<true, false>(p, st);
 }
 
 }  // namespace kfa
