@@ -52,7 +52,7 @@ struct FwdShared {
 // 192 threads: warps 0-3 softmax (thread <-> query row), warp 4 MMA issuer, warp 5 loader.
 // Tensor memory (256 columns): S at 0 (rd(p) overwrites its first 64 columns), O at 128, the
 // residual weights at 192.
-template <bool BF16>
+template <bool BF16, bool TWO>
 __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ NaMaps maps, AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -128,8 +128,10 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
             int pos = 0, iter = 0;
             for (int j = next_tile(sh.bitmap, 0); j >= 0 && ok; j = next_tile(sh.bitmap, j + 1)) {
                 const int ks = pos % kRing;
+                KFA_TRACE_POINT(0, 1);
                 ok = mbar_wait(&sh.full[ks], (pos / kRing) & 1, abort_word, 21);
                 if (!ok) break;
+                KFA_TRACE_POINT(0, 2);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
@@ -140,14 +142,16 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
                 ++pos;
                 const int vs = pos % kRing;
                 ok = mbar_wait(&sh.full[vs], (pos / kRing) & 1, abort_word, 22);
+                KFA_TRACE_POINT(0, 3);
                 if (ok) ok = mbar_wait(&sh.p_ready, iter & 1, abort_word, 23);
                 if (!ok) break;
+                KFA_TRACE_POINT(0, 4);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk)
                     umma_ts(tmem + 128, tmem + kk * 8, umma_desc_advance(v_desc, vs * kChunkBytes + kk * 2048), idesc_o,
                             iter > 0 || kk > 0);
-                if (p.two_term) {
+                if (TWO) {
 #pragma unroll
                     for (int kk = 0; kk < kTile / 16; ++kk)
                         umma_ts(tmem + 128, tmem + 192 + kk * 8, umma_desc_advance(v_desc, vs * kChunkBytes + kk * 2048),
@@ -169,20 +173,37 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
         bool ok = true;
         for (int j = next_tile(sh.bitmap, 0); j >= 0 && ok; j = next_tile(sh.bitmap, j + 1)) {
             uint32_t vis[4] = {0, 0, 0, 0};
+            KFA_TRACE_POINT(1, 1);
             if (row_ok) box_mask<4>(p, box, j * kTile, p.Sk, vis);
+            KFA_TRACE_POINT(1, 2);
             ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 30);
             if (!ok) break;
+            KFA_TRACE_POINT(1, 3);
             tc_fence_after();
-            // pass 1: maximum over the visible scores of this tile
-            float mx = -INFINITY;
+            // pass 1: hide what the row does not see (written back as -inf), maximum of the rest
+            // 32-column chunks that no row of this warp can see are skipped (their weights are zero)
+            uint32_t live = 0;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) live |= (__any_sync(0xffffffffu, vis[c] != 0) ? 1u : 0u) << c;
+            float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
+                if (!((live >> c) & 1u)) continue;
                 uint32_t r[32];
                 tmem_ld32(s_addr + c * 32, r);
                 tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (vis[c] >> i) & 1u ? __uint_as_float(r[i]) : -INFINITY);
+                for (int i = 0; i < 32; i += 2) {
+                    r[i] = hide(r[i], vis[c], i);
+                    r[i + 1] = hide(r[i + 1], vis[c], i + 1);
+                    mx0 = fmaxf(mx0, __uint_as_float(r[i]));
+                    mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
+                }
+                tmem_st32(s_addr + c * 32, r);
             }
+            const float mx = fmaxf(mx0, mx1);
+            tmem_wait_st();
+            KFA_TRACE_POINT(1, 4);
             m_true = fmaxf(m_true, mx);
             const bool rebase = mx > m_used && (m_used == -INFINITY || (mx - m_used) * c2 > kRebase);
             float alpha = 1.f;
@@ -202,34 +223,50 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
                     tmem_st32(o_addr + c, r);
                 }
             }
-            // pass 2: weights, their rounding (and its residual), the normaliser
+            // pass 2: weights (hidden scores give exact zeros), their rounding and its residual, the normaliser
             const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-            float sum0 = 0.f, sum1 = 0.f;
+            const uint64_t m_pair = f2_pack(m_safe, m_safe), c2_pair = f2_pack(c2, c2);
+            uint64_t sum = f2_pack(0.f, 0.f);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t r[32], hi[16], lo[16];
+                if (!((live >> c) & 1u)) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) hi[i] = 0;
+                    tmem_st16(s_addr + c * 16, hi);
+                    if (TWO) tmem_st16(lo_addr + c * 16, hi);
+                    continue;
+                }
                 tmem_ld32(s_addr + c * 32, r);
                 tmem_wait_ld();
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float pa = ex2((__uint_as_float(r[i]) - m_safe) * c2);
-                    float pb = ex2((__uint_as_float(r[i + 1]) - m_safe) * c2);
-                    pa = (vis[c] >> i) & 1u ? pa : 0.f;
-                    pb = (vis[c] >> (i + 1)) & 1u ? pb : 0.f;
-                    sum0 += pa;
-                    sum1 += pb;
+                    float pa, pb;
+                    f2_unpack(f2_mul(f2_sub(f2_pack(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), m_pair), c2_pair),
+                              pa, pb);
+                    pa = ex2(pa);
+                    pb = ex2(pb);
+                    const uint64_t pp = f2_pack(pa, pb);
+                    sum = f2_add(sum, pp);
                     const uint32_t w = pack2<BF16>(pa, pb);
                     hi[i / 2] = w;
-                    const float2 back = unpack2<BF16>(w);
-                    lo[i / 2] = pack2<BF16>(pa - back.x, pb - back.y);
+                    if (TWO) {
+                        const float2 back = unpack2<BF16>(w);
+                        float ra, rb;
+                        f2_unpack(f2_sub(pp, f2_pack(back.x, back.y)), ra, rb);
+                        lo[i / 2] = pack2<BF16>(ra, rb);
+                    }
                 }
                 tmem_st16(s_addr + c * 16, hi);
-                if (p.two_term) tmem_st16(lo_addr + c * 16, lo);
+                if (TWO) tmem_st16(lo_addr + c * 16, lo);
             }
+            float sum0, sum1;
+            f2_unpack(sum, sum0, sum1);
             l += sum0 + sum1;
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&sh.p_ready);
+            KFA_TRACE_POINT(1, 5);
             ++iter;
         }
         if (iter > 0 && ok) ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 31);
@@ -425,7 +462,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
             row_dl = p.delta[stat0 + row];
             if (row_m == -INFINITY) row_m = INFINITY;
         }
-        float sum_ds = 0.f, mass = 0.f, t_num = 0.f, t_den = 0.f;
+        uint64_t acc_ds = f2_pack(0.f, 0.f), acc_mass = acc_ds, acc_num = acc_ds, acc_den = acc_ds;
         const int tid = warp * 32 + lane;
         int n = 0;
         bool ok = true;
@@ -455,43 +492,59 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
             if (!ok) break;
             tc_fence_after();
             const float* stat = &sh.stats[n & 1][0][0];
+            const uint64_t c2_pair = f2_pack(c2, c2);
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 uint32_t s[32], dp[32], w0[16], w1[16];
+                if (!__any_sync(0xffffffffu, vis[half] != 0)) {
+                    // no row of this warp sees these 32 partners: both operands are zero
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) w0[i] = 0;
+                    tmem_st16(lane_base + half * 16, w0);
+                    tmem_st16(lane_base + 64 + half * 16, w0);
+                    continue;
+                }
                 tmem_ld32(lane_base + half * 32, s);
                 tmem_ld32(lane_base + 64 + half * 32, dp);
                 tmem_wait_ld();
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    float m = row_m, ls = row_ls, dl = row_dl, tt = 0.f;
+                for (int c = 0; c < 32; c += 2) {
+                    uint64_t m2, ls2, dl2;
                     if (KV) {
-                        m = stat[half * 32 + c];
-                        ls = stat[kSub + half * 32 + c];
-                        dl = stat[2 * kSub + half * 32 + c];
-                        tt = stat[3 * kSub + half * 32 + c];
+                        const float2 mm = *reinterpret_cast<const float2*>(stat + half * 32 + c);
+                        const float2 ll = *reinterpret_cast<const float2*>(stat + kSub + half * 32 + c);
+                        const float2 dd = *reinterpret_cast<const float2*>(stat + 2 * kSub + half * 32 + c);
+                        const float2 tt = *reinterpret_cast<const float2*>(stat + 3 * kSub + half * 32 + c);
+                        m2 = f2_pack(mm.x, mm.y);
+                        ls2 = f2_pack(ll.x, ll.y);
+                        dl2 = f2_pack(dd.x + tt.x, dd.y + tt.y);  // (dP - delta) - t, both belong to the query
+                    } else {
+                        m2 = f2_pack(row_m, row_m);
+                        ls2 = f2_pack(row_ls, row_ls);
+                        dl2 = f2_pack(row_dl, row_dl);
                     }
-                    float p32 = ex2((__uint_as_float(s[c]) - m) * c2 - ls);
-                    p32 = (vis[half] >> c) & 1u ? p32 : 0.f;
-                    const float res = __uint_as_float(dp[c]) - dl;
-                    const float pl = round_low<T>(p32);
-                    // a hidden entry contributes an exact zero whatever dP holds
-                    const float prod = p32 == 0.f ? 0.f : p32 * (KV ? res - tt : res);
-                    const float ds = round_low<T>(prod);
+                    // hidden entries: score -inf, so P32 is an exact zero and so is everything built from it
+                    const uint64_t sc = f2_pack(__uint_as_float(hide(s[c], vis[half], c)),
+                                                __uint_as_float(hide(s[c + 1], vis[half], c + 1)));
+                    float ea, eb;
+                    f2_unpack(f2_sub(f2_mul(f2_sub(sc, m2), c2_pair), ls2), ea, eb);
+                    const uint64_t p32 = f2_pack(ex2(ea), ex2(eb));
+                    const uint64_t prod =
+                        f2_mul(p32, f2_sub(f2_pack(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), dl2));
+                    float pa, pb, da, db;
+                    f2_unpack(p32, pa, pb);
+                    f2_unpack(prod, da, db);
+                    const uint32_t pl = pack2<BF16>(pa, pb), ds = pack2<BF16>(da, db);
                     if (!KV) {
-                        sum_ds += ds;
-                        mass += pl;
-                        t_num += prod;
-                        t_den += p32;
+                        const float2 plf = unpack2<BF16>(pl), dsf = unpack2<BF16>(ds);
+                        acc_ds = f2_add(acc_ds, f2_pack(dsf.x, dsf.y));
+                        acc_mass = f2_add(acc_mass, f2_pack(plf.x, plf.y));
+                        acc_num = f2_add(acc_num, prod);
+                        acc_den = f2_add(acc_den, p32);
                     }
                     // 16-bit operands: over S goes dS_q (query owners) / rd(P32) (key owners); over dP the other
-                    const float over_s = KV ? pl : ds, over_dp = KV ? ds : pl;
-                    s[c] = __float_as_uint(over_s);
-                    dp[c] = __float_as_uint(over_dp);
-                }
-#pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    w0[c / 2] = pack2<BF16>(__uint_as_float(s[c]), __uint_as_float(s[c + 1]));
-                    w1[c / 2] = pack2<BF16>(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1]));
+                    w0[c / 2] = KV ? pl : ds;
+                    w1[c / 2] = KV ? ds : pl;
                 }
                 tmem_st16(lane_base + half * 16, w0);
                 tmem_st16(lane_base + 64 + half * 16, w1);
@@ -512,6 +565,15 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
             } else {
                 out0 = reinterpret_cast<T*>(p.dq) + (int64_t)b * p.dqs[0] + (int64_t)h * p.dqs[1] + (int64_t)r * p.dqs[2];
             }
+            float u0, u1;
+            f2_unpack(acc_ds, u0, u1);
+            const float sum_ds = u0 + u1;
+            f2_unpack(acc_mass, u0, u1);
+            const float mass = u0 + u1;
+            f2_unpack(acc_num, u0, u1);
+            const float t_num = u0 + u1;
+            f2_unpack(acc_den, u0, u1);
+            const float t_den = u0 + u1;
             const float ratio = mass != 0.f ? sum_ds / mass : 0.f;
 #pragma unroll
             for (int c = 0; c < 64; c += 32) {
@@ -573,12 +635,16 @@ bool encode_all(NaMaps* maps, const AttnParams& p, bool bf16, bool backward, int
 
 template <bool BF16>
 cudaError_t forward_t(const AttnParams& p, cudaStream_t st) {
-    cudaError_t e = cudaFuncSetAttribute(na_tc_forward<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
+    auto kernel = p.two_term ? na_tc_forward<BF16, true> : na_tc_forward<BF16, false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
+    if (e != cudaSuccess) return e;
+    // two CTAs per SM need the largest shared-memory carve-out
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
     NaMaps maps;
     if (!encode_all(&maps, p, BF16, false, kTile)) return cudaErrorInvalidValue;
     const int64_t grid = (int64_t)((p.Sq + kTile - 1) / kTile) * p.B * p.Hq;
-    na_tc_forward<BF16><<<(unsigned)grid, 192, kFwdSmem, st>>>(maps, p);
+    kernel<<<(unsigned)grid, 192, kFwdSmem, st>>>(maps, p);
     return cudaGetLastError();
 }
 
@@ -586,6 +652,9 @@ template <bool KV, bool BF16>
 cudaError_t backward_t(const AttnParams& p, cudaStream_t st) {
     cudaError_t e =
         cudaFuncSetAttribute(na_tc_backward<KV, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(na_tc_backward<KV, BF16>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
     const CUtensorMapDataType dt = BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     BwdMaps maps;
@@ -638,5 +707,16 @@ cudaError_t launch_na_pipeline_backward(const AttnParams& p, bool bf16, int whic
     if (which == 0) return bf16 ? backward_t<false, true>(p, st) : backward_t<false, false>(p, st);
     return bf16 ? backward_t<true, true>(p, st) : backward_t<true, false>(p, st);
 }
+
+#ifdef KFA_TRACE
+extern "C" __attribute__((visibility("default"))) int kfa_debug_trace_na(long long* out, int* counts) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_kfa_trace, sizeof(long long) * 4 * 1024);
+    cudaMemcpyFromSymbol(counts, g_kfa_trace_n, sizeof(int) * 4);
+    int zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_kfa_trace_n, zero, sizeof(zero));
+    return 0;
+}
+#endif
 
 }  // namespace kfa

@@ -68,24 +68,38 @@ __device__ __forceinline__ int next_tile(const uint32_t* bitmap, int j) {
 }
 
 // Bit c of the result (word c / 32) is set when partner token tok0 + c lies in the box.
-// `limit` is the length of the partner sequence.
+// `limit` is the length of the partner sequence.  The tile is walked grid row by grid row (two integer
+// divisions per call, none per row).
 template <int WORDS>
 __device__ __forceinline__ void box_mask(const AttnParams& p, const Box& b, int tok0, int limit, uint32_t (&m)[WORDS]) {
 #pragma unroll
     for (int w = 0; w < WORDS; ++w) m[w] = 0;
     const int ex = p.ext[2], ey = p.ext[1];
-    const int r_first = tok0 / ex, r_last = (min(tok0 + 32 * WORDS, limit) - 1) / ex;
-    for (int r = r_first; r <= r_last; ++r) {
-        const int z = r / ey, y = r - z * ey;
-        if (z < b.zlo || z > b.zhi || y < b.ylo || y > b.yhi) continue;
-        const int lo = max(r * ex + b.xlo - tok0, 0), hi = min(r * ex + b.xhi - tok0, 32 * WORDS - 1);
-        if (lo > hi) continue;
+    const int last = min(tok0 + 32 * WORDS, limit) - 1 - tok0;  // last bit that is a real token
+    const int r = tok0 / ex;
+    int z = r / ey, y = r - z * ey;
+    for (int base = r * ex - tok0; base <= last; base += ex) {  // bit index of the row's x = 0
+        if (z >= b.zlo && z <= b.zhi && y >= b.ylo && y <= b.yhi) {
+            const int lo = max(base + b.xlo, 0), hi = min(base + b.xhi, 32 * WORDS - 1);
+            if (lo <= hi) {
 #pragma unroll
-        for (int w = 0; w < WORDS; ++w) {
-            const int a = max(lo - 32 * w, 0), e = min(hi - 32 * w, 31);
-            if (a <= e) m[w] |= static_cast<uint32_t>(((1ull << (e - a + 1)) - 1ull) << a);
+                for (int w = 0; w < WORDS; ++w) {
+                    const int a = max(lo - 32 * w, 0), e = min(hi - 32 * w, 31);
+                    if (a <= e) m[w] |= (0xffffffffu >> (31 - (e - a))) << a;
+                }
+            }
+        }
+        if (++y == ey) {
+            y = 0;
+            ++z;
         }
     }
+}
+
+// -inf where bit `i` of `vis` is clear, the score itself where it is set.
+__device__ __forceinline__ uint32_t hide(uint32_t score_bits, uint32_t vis, int i) {
+    const uint32_t keep = static_cast<uint32_t>(static_cast<int32_t>(vis << (31 - i)) >> 31);
+    return (score_bits & keep) | (~keep & 0xff800000u);
 }
 
 }  // namespace na
