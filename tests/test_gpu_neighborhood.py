@@ -115,3 +115,59 @@ def test_compiled_neighborhood_with_equal_length_different_geometry():
     compiled = torch.compile(fn)
     for spatial, window in (((6, 10), (3, 3)), ((10, 6), (3, 3)), ((3, 4, 5), (3, 3, 3))):
         torch.testing.assert_close(compiled(q, k, v, spatial, window), fn(q, k, v, spatial, window), atol=0, rtol=0)
+
+
+# ------------------------------------------------ tensor-core family against the window-enumerating family
+def _kernel_names(fn):
+    from kohakufa_cute import native
+
+    native.profile_read(reset=True)
+    native.profile_enable(True)
+    try:
+        result = fn()
+        torch.cuda.synchronize()
+    finally:
+        native.profile_enable(False)
+    return result, set(native.profile_read(reset=True))
+
+
+def _run_misaligned(q, k, v, dout, spatial, window, scale):
+    """Same values behind views whose rows start 8 bytes off a 16-byte boundary: the tensor-memory
+    kernels cannot address them, so the exact-window CUDA-core kernels run."""
+    wides = []
+    for t in (q, k, v):
+        wide = torch.zeros(*t.shape[:-1], t.shape[-1] + 8, device=t.device, dtype=t.dtype)
+        wide[..., 4:4 + t.shape[-1]] = t
+        wides.append(wide.requires_grad_(True))
+    views = [w[..., 4:4 + q.shape[-1]] for w in wides]
+    out = api().neighborhood_attention(*views, spatial_shape=spatial, window_size=window, scale=scale)
+    grads = torch.autograd.grad(out, wides, dout)
+    return (out.detach(), *[g[..., 4:4 + q.shape[-1]] for g in grads])
+
+
+@pytest.mark.parametrize("spatial,window,dtype", (((16, 32, 32), (3, 7, 7), torch.float16),
+                                                  ((5, 32, 32), (3, 7, 7), torch.bfloat16),
+                                                  ((64, 64), (7, 7), torch.bfloat16),
+                                                  ((3, 17, 29), (3, 5, 9), torch.float16)))
+def test_tensor_core_family_matches_window_enumeration_at_full_size(spatial, window, dtype):
+    """The benchmark's 16x32x32 / (3,7,7) grid (and the reference's published shapes): the dense-tile
+    tensor-core kernels and the exact-window kernels follow one arithmetic contract, so their results
+    agree to accumulation-order noise; the small-grid tests pin both to the oracle."""
+    gen = torch.Generator().manual_seed(len(spatial) * 100 + spatial[-1])
+    tokens = 1
+    for n in spatial:
+        tokens *= n
+    heads = 4 if tokens > 8192 else 2
+    q, k, v, dout = (torch.randn(1, heads, tokens, 64, generator=gen).to(dtype).cuda() for _ in range(4))
+    fast, fast_names = _kernel_names(lambda: run(q, k, v, dout, spatial, window, 0.125))
+    slow, slow_names = _kernel_names(lambda: _run_misaligned(q, k, v, dout, spatial, window, 0.125))
+    assert {"na_pipeline_forward", "na_pipeline_backward_q", "na_pipeline_backward_kv"} <= fast_names
+    assert {"neighborhood_forward", "neighborhood_backward_q", "neighborhood_backward_kv"} <= slow_names
+    from kohakufa_cute import native
+
+    assert native.device_status(reset=True) == 0
+    for name, a, b in zip(NAMES, fast, slow):
+        assert bool(torch.isfinite(a).all()), name
+        # two roundings to the 16-bit type of (almost) the same FP32 value differ by at most one ulp
+        assert ao.per_head_relative_error(a.cpu(), b.cpu().double()) < 0.5 * TOL[dtype]["norm"], name
+        torch.testing.assert_close(a.float(), b.float(), atol=TOL[dtype]["elem"], rtol=TOL[dtype]["elem"])
