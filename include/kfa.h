@@ -86,7 +86,10 @@ KFA_API int kfa_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tens
 KFA_API int kfa_pack_mask(const kfa_tensor* mask, kfa_tensor* blocks, void* stream);
 
 /* Bytes of scratch kfa_backward needs for these shapes (native.cpp:341-354 sizes the
- * same buffers: delta and its base). */
+ * same buffers: delta and its base).  For heads of 256, 384 or 512 channels the figure also
+ * covers two 16-bit [B,Hq,Sq,ceil128(Sk)] matrices (rounded probabilities and score gradients)
+ * that the wide-head tensor-core backward stores once and multiplies three times; when one
+ * matrix would exceed 4 GiB they are left out and the general kernels run. */
 KFA_API size_t kfa_backward_workspace_bytes(const kfa_tensor* q, const kfa_tensor* k);
 
 /*
@@ -179,7 +182,8 @@ KFA_API void kfa_profile_reset(void);
 KFA_API int kfa_device_status(int reset);
 
 /* Which kernel family kfa_forward / kfa_backward would select for these operands:
- * 0 = general kernels, 1 = tcgen05 tensor-memory pipeline.  (The reference exposes its
+ * 0 = general kernels, 1 = tcgen05 tensor-memory pipeline (heads of 64/128 channels),
+ * 2 = tcgen05 wide-head kernels (256/384/512 channels).  (The reference exposes its
  * selection through kernels.kernel_configuration, kernels.py:2593-2637.) */
 KFA_API int kfa_selected_family(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v,
                         const kfa_tensor* mask, int causal, int backward);
