@@ -39,6 +39,12 @@ WORKLOADS = {
                       graph=True, published_tflops=214.7),
     "dit_masked": dict(B=2, Hq=24, Hkv=24, S=32768, D=128, dtype="bf16", causal=False, center_keys=False, seed=4,
                        masked_fraction=0.1),
+    # BASELINE config 4, second part: one long sequence sharded over the ranks (ring context parallelism).
+    # The sequence is divided by the number of ranks, so the job is fixed as N grows (strong scaling).
+    "dit_ring": dict(B=1, Hq=24, Hkv=24, S=262144, D=128, dtype="bf16", causal=False, center_keys=False, seed=6,
+                     masked_fraction=0.1, ring=True),
+    "dit_ring_small": dict(B=1, Hq=24, Hkv=24, S=65536, D=128, dtype="bf16", causal=False, center_keys=False, seed=6,
+                           masked_fraction=0.1, ring=True),
     "neighborhood_3d": dict(B=1, Hq=16, Hkv=16, S=16 * 32 * 32, D=64, dtype="fp16", causal=False, center_keys=False,
                             seed=5, grid=(16, 32, 32), window=(3, 7, 7)),
 }
@@ -56,11 +62,16 @@ def algorithmic_flops(w):
     return 3.5 * 4 * w["B"] * w["Hq"] * w["D"] * pairs
 
 
-def make_host_inputs(w, rank):
-    """Seeded synthetic q, k, v, dO (and mask) in pinned host memory."""
+def make_host_inputs(w, rank, world=1):
+    """Seeded synthetic q, k, v, dO (and mask) in pinned host memory.  Ring workloads get this rank's
+    contiguous shard of the sequence (and of the key-padding mask)."""
     dtype = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
     gen = torch.Generator().manual_seed(w["seed"] * 1000 + rank)
     B, Hq, Hkv, S, D = w["B"], w["Hq"], w["Hkv"], w["S"], w["D"]
+    total, first = S, 0
+    if w.get("ring"):
+        S = total // world
+        first = rank * S
 
     def randn(*shape):
         out = torch.empty(shape, dtype=torch.float32)
@@ -80,15 +91,20 @@ def make_host_inputs(w, rank):
     tensors = [t.to(dtype).pin_memory() for t in (q, k, v, g)]
     mask = None
     if "masked_fraction" in w:
-        keep = S - int(S * w["masked_fraction"] + 0.5)
-        mask = (torch.arange(S) < keep)[None, None, None, :].expand(B, 1, 1, S).contiguous().pin_memory()
+        keep = total - int(total * w["masked_fraction"] + 0.5)
+        mask = (torch.arange(first, first + S) < keep)[None, None, None, :].expand(B, 1, 1, S).contiguous().pin_memory()
     return tensors, mask
 
 
 def build_step(w):
     import kohakufa_cute
 
-    if "window" in w:
+    if w.get("ring"):
+        from kohakufa_cute import parallel
+
+        def forward(q, k, v, mask):
+            return parallel.ring_attention(q, k, v, key_mask=mask)
+    elif "window" in w:
         grid, window = w["grid"], w["window"]
 
         def forward(q, k, v, mask):
@@ -231,10 +247,15 @@ def main():
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+    elif w.get("ring"):
+        # the ring layer talks to torch.distributed even when it has a single member
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29531")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
 
-    (hq, hk, hv, hg), hmask = make_host_inputs(w, rank)
+    (hq, hk, hv, hg), hmask = make_host_inputs(w, rank, world)
     step = build_step(w)
     dq_, dk_, dv_, dg_ = (t.to(device).requires_grad_(i < 3) for i, t in enumerate((hq, hk, hv, hg)))
     dmask = None if hmask is None else hmask.to(device)
@@ -339,8 +360,9 @@ def main():
     elapsed_ms, e2e_ms = (float(x) for x in times.cpu())
 
     flops = algorithmic_flops(w)
-    value = flops * steps * world / (elapsed_ms * 1e-3) / 1e12
-    e2e_value = flops * e2e_steps * world / (e2e_ms * 1e-3) / 1e12
+    jobs = 1 if w.get("ring") else world  # a ring step is ONE job shared by all ranks
+    value = flops * steps * jobs / (elapsed_ms * 1e-3) / 1e12
+    e2e_value = flops * e2e_steps * jobs / (e2e_ms * 1e-3) / 1e12
     h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hg)) + (0 if hmask is None else hmask.numel())
     d2h = sum(t.numel() * t.element_size() for t in host_out)
 
@@ -357,7 +379,9 @@ def main():
                      "wide_grad_v": 1.0}.get(name)
             if share is None:
                 share = 1.5 if name.endswith("_q") else 3.5
-            per_launch = flops * share / 7.0
+            prof_steps = 3 if use_graph else steps
+            per_step = max(1, int(round(count / prof_steps)))  # a ring step launches each kernel once per block
+            per_launch = flops / (world if w.get("ring") else 1) * share / 7.0 / per_step
             achieved = per_launch / (total_ms / count * 1e-3) / 1e12
             peak = sustained or burst
             roofline = {"bound": "tensor", "kernel": name, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
@@ -371,11 +395,13 @@ def main():
                    "sample": sample, "seconds": cpu_seconds}
         line = {
             "metric": "attn fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
-            "warmup": warmup, "ms_per_step": elapsed_ms / steps, "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": elapsed_ms / steps, "higher_is_better": True,
+            "scaling": "strong" if w.get("ring") else "weak",
             "vs_baseline": (value / world / w["published_tflops"]) if "published_tflops" in w else None,
             "dtype": w["dtype"], "data": "synthetic",
             "config": {"workload": w["name"], "launch": "cuda_graph" if use_graph else "eager", "B": w["B"], "Hq": w["Hq"], "Hkv": w["Hkv"], "S": w["S"], "D": w["D"],
-                       "causal": w["causal"], "center_keys": w["center_keys"], "sharding": f"replica-per-gpu x{world}",
+                       "causal": w["causal"], "center_keys": w["center_keys"], "sharding": (f"ring context parallel, S/{world} per rank" if w.get("ring")
+                                    else f"replica-per-gpu x{world}"),
                        "l2": "inputs larger than L2 (q+k+v+dO+O > 126 MB)" if h2d > 126e6 else (
                            f"steps rotate over {rotation} input sets, together larger than L2" if rotation > 1
                            else "inputs fit in L2"),

@@ -66,13 +66,18 @@ struct FwdShared {
     uint64_t empty[kRing];
     uint64_t s_ready;
     uint64_t p_ready;
+    uint64_t pvb_done;
     uint32_t tmem_base;
     int abort_word;
 };
 
 // maps.a = Q, maps.b = K, maps.c = V.  256 threads: warps 0-3 softmax (thread <-> query row),
-// warp 4 MMA issuer, warp 5 loader.  Tensor memory: S at column 0 (P_low overwrites its first 64
-// columns), O[:, half] at column 256.
+// warps 4 and 6 MMA issuers, warp 5 loader.  A tcgen05.mma holds its issuing thread for about a
+// hundred cycles whatever its size, and a 512-channel score tile needs 32 of them, so the scores are
+// formed by TWO issuers into two partial accumulators: issuer 0 contracts the even 64-channel chunks
+// into S_a (column 0), issuer 1 the odd ones into S_b (column 128); the softmax adds the two.  Each
+// issuer then forms its share of the output channels of O[:, half] (column 256) from P_low, which
+// overwrites the first 64 columns of S_a.
 template <bool BF16>
 __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ WideMaps maps, AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -103,8 +108,9 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
             mbar_init(&sh.full[i], 1);
             mbar_init(&sh.empty[i], 1);
         }
-        mbar_init(&sh.s_ready, 1);
+        mbar_init(&sh.s_ready, 2);  // both issuers
         mbar_init(&sh.p_ready, kTile);
+        mbar_init(&sh.pvb_done, 1);
         mbar_fence_init();
     }
     if (warp == 4) {
@@ -143,22 +149,29 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
                 }
             }
         }
-    } else if (warp == 4) {
-        // ------------------------------------------------------------ MMA issuer
+    } else if (warp == 4 || warp == 6) {
+        // ----------------------------------------------------------- MMA issuers
         if (lane == 0) {
+            const int who = warp == 4 ? 0 : 1;
             const uint32_t idesc_s =
                 umma_idesc(kTile, kTile, BF16 ? 1 : 0, false, false) | (p.scale < 0.f ? kUmmaNegateA : 0u);
-            const uint32_t idesc_o = umma_idesc(kTile, 64 * hc, BF16 ? 1 : 0, false, true);
+            // output channels of this CTA are split between the issuers by V chunk
+            const int ha = (hc + 1) / 2;
+            const int v_first = who == 0 ? 0 : ha, v_count = who == 0 ? ha : hc - ha;
+            const uint32_t idesc_o = umma_idesc(kTile, 64 * v_count, BF16 ? 1 : 0, false, true);
             const uint64_t q_desc = umma_desc_sw128(smem_u32(sQ), 16, 1024);
             const uint64_t k_desc = umma_desc_sw128(smem_u32(sRing), 16, 1024);
-            // V chunks of one tile sit in consecutive slots: N = 64 * hc channels per instruction
+            // the V chunks of one tile sit in consecutive slots: one instruction spans an issuer's share
             const uint64_t v_desc = umma_desc_sw128(smem_u32(sRing), kChunkBytes, 1024);
             bool ok = mbar_wait(&sh.q_full, 0, abort_word, 20);
             int pos = 0, iter = 0;
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (key_tile_state(p, b, h, j) == 0) continue;
+                // S_a also holds P_low of the previous tile, which issuer 1's product is still reading
+                if (who == 0 && iter > 0) ok = mbar_wait(&sh.pvb_done, (iter - 1) & 1, abort_word, 24);
                 KFA_TRACE_POINT(0, 1);
                 for (int c = 0; c < chunks && ok; ++c, ++pos) {
+                    if ((c & 1) != who) continue;
                     const int slot = pos % kRing;
                     ok = mbar_wait(&sh.full[slot], (pos / kRing) & 1, abort_word, 21);
                     if (!ok) break;
@@ -166,25 +179,29 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
-                        umma_ss(tmem, umma_desc_advance(q_desc, c * kChunkBytes + kk * 32),
-                                umma_desc_advance(k_desc, slot * kChunkBytes + kk * 32), idesc_s, c > 0 || kk > 0);
+                        umma_ss(tmem + who * 128, umma_desc_advance(q_desc, c * kChunkBytes + kk * 32),
+                                umma_desc_advance(k_desc, slot * kChunkBytes + kk * 32), idesc_s, c > who || kk > 0);
                     umma_commit(&sh.empty[slot]);
                 }
                 if (!ok) break;
                 umma_commit(&sh.s_ready);
-                const int s0 = pos % kRing;
-                for (int i = 0; i < hc && ok; ++i)
-                    ok = mbar_wait(&sh.full[(pos + i) % kRing], ((pos + i) / kRing) & 1, abort_word, 22);
+                const int s0 = (pos + v_first) % kRing;
+                for (int i = 0; i < v_count && ok; ++i)
+                    ok = mbar_wait(&sh.full[(pos + v_first + i) % kRing], ((pos + v_first + i) / kRing) & 1, abort_word,
+                                   22);
                 KFA_TRACE_POINT(0, 3);
                 if (ok) ok = mbar_wait(&sh.p_ready, iter & 1, abort_word, 23);
                 if (!ok) break;
                 KFA_TRACE_POINT(0, 4);
                 tc_fence_after();
+                if (v_count > 0) {
 #pragma unroll
-                for (int kk = 0; kk < kTile / 16; ++kk)
-                    umma_ts(tmem + 256, tmem + kk * 8, umma_desc_advance(v_desc, s0 * kChunkBytes + kk * 2048), idesc_o,
-                            iter > 0 || kk > 0);
-                for (int i = 0; i < hc; ++i) umma_commit(&sh.empty[(pos + i) % kRing]);
+                    for (int kk = 0; kk < kTile / 16; ++kk)
+                        umma_ts(tmem + 256 + v_first * 64, tmem + kk * 8,
+                                umma_desc_advance(v_desc, s0 * kChunkBytes + kk * 2048), idesc_o, iter > 0 || kk > 0);
+                }
+                for (int i = 0; i < v_count; ++i) umma_commit(&sh.empty[(pos + v_first + i) % kRing]);
+                if (who == 1) umma_commit(&sh.pvb_done);
                 pos += hc;
                 ++iter;
             }
@@ -214,12 +231,13 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
             float s[kTile];
 #pragma unroll
             for (int c = 0; c < kTile; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(s_addr + c, r);
+                uint32_t ra[32], rb[32];
+                tmem_ld32(s_addr + c, ra);
+                tmem_ld32(s_addr + 128 + c, rb);
+                tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(r[i]);
+                for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(ra[i]) + __uint_as_float(rb[i]);
             }
-            tmem_wait_ld();
             const int key0 = j * kTile;
             int lim = p.Sk - key0;
             if (p.causal) lim = min(lim, row - key0 + 1);
@@ -360,8 +378,9 @@ struct ScoreShared {
 
 // MODE 0: maps.a = Q (resident), maps.b = K (streamed); writes P_low.
 // MODE 1: maps.a = dO (resident), maps.b = V (streamed); reads P_low, writes dS_low.
-// 256 threads: warps 0-3 consumers (thread <-> query row), warp 4 MMA issuer, warp 5 loader.
-// Two score buffers in tensor memory (columns 0 and 128) let the tensor core run one tile ahead.
+// 256 threads: warps 0-3 consumers (thread <-> query row), warps 4 and 6 MMA issuers, warp 5 loader.
+// Two score buffers in tensor memory (columns 0 and 256, each a pair of partial accumulators) let the
+// tensor core run one tile ahead.
 template <int MODE, bool BF16>
 __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ WideMaps maps, AttnParams p, Stored st) {
     extern __shared__ uint8_t smem_raw[];
@@ -391,13 +410,13 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
             mbar_init(&sh.empty[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&sh.s_ready[i], 1);
+            mbar_init(&sh.s_ready[i], 2);  // both issuers
             mbar_init(&sh.s_free[i], kTile);
         }
         mbar_fence_init();
     }
     if (warp == 4) {
-        tmem_alloc(&sh.tmem_base, 256);
+        tmem_alloc(&sh.tmem_base, 512);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -424,8 +443,11 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
                     tma_load_4d(sRing + slot * kChunkBytes, &maps.b, &sh.full[slot], c * 64, j * kTile, kvh, b);
                 }
         }
-    } else if (warp == 4) {
+    } else if (warp == 4 || warp == 6) {
+        // Two issuers share the contraction: issuer 0 the even 64-channel chunks, issuer 1 the odd ones,
+        // each into its own partial accumulator (columns +0 and +128 of the score buffer).
         if (lane == 0) {
+            const int who = warp == 4 ? 0 : 1;
             const uint32_t idesc = umma_idesc(kTile, kTile, BF16 ? 1 : 0, false, false) |
                                    (MODE == 0 && p.scale < 0.f ? kUmmaNegateA : 0u);
             const uint64_t a_desc = umma_desc_sw128(smem_u32(sOwn), 16, 1024);
@@ -438,14 +460,15 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
                 if (!ok) break;
                 tc_fence_after();
                 for (int c = 0; c < chunks && ok; ++c, ++pos) {
+                    if ((c & 1) != who) continue;
                     const int slot = pos % kRing;
                     ok = mbar_wait(&sh.full[slot], (pos / kRing) & 1, abort_word, 43);
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
-                        umma_ss(tmem + buf * 128, umma_desc_advance(a_desc, c * kChunkBytes + kk * 32),
-                                umma_desc_advance(b_desc, slot * kChunkBytes + kk * 32), idesc, c > 0 || kk > 0);
+                        umma_ss(tmem + buf * 256 + who * 128, umma_desc_advance(a_desc, c * kChunkBytes + kk * 32),
+                                umma_desc_advance(b_desc, slot * kChunkBytes + kk * 32), idesc, c > who || kk > 0);
                     umma_commit(&sh.empty[slot]);
                 }
                 if (ok) umma_commit(&sh.s_ready[buf]);
@@ -487,12 +510,13 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
             float s[kTile];
 #pragma unroll
             for (int c = 0; c < kTile; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(lane_base + buf * 128 + c, r);
+                uint32_t ra[32], rb[32];
+                tmem_ld32(lane_base + buf * 256 + c, ra);
+                tmem_ld32(lane_base + buf * 256 + 128 + c, rb);
+                tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(r[i]);
+                for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(ra[i]) + __uint_as_float(rb[i]);
             }
-            tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(&sh.s_free[buf]);
             if (!row_ok) continue;
@@ -545,7 +569,7 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 3100 + sh.abort_word;
-    if (warp == 4) tmem_dealloc(tmem, 256);
+    if (warp == 4) tmem_dealloc(tmem, 512);
 }
 
 // ------------------------------------------------------------------- backward: gradient products
