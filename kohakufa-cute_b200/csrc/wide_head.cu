@@ -123,20 +123,27 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
     const uint32_t tmem = sh.tmem_base;
     volatile int* abort_word = &sh.abort_word;
 
-    if (warp == 5) {
-        // ---------------------------------------------------------------- loader
+    if (warp == 5 || warp == 7) {
+        // --------------------------------------------------------------- loaders
+        // Two loading threads take alternate ring positions: one thread's stream of 16 KB boxes does not
+        // keep the ring full.
         if (lane == 0) {
+            const int me = warp == 5 ? 0 : 1;
             tma_prefetch_desc(&maps.a);
             tma_prefetch_desc(&maps.b);
             tma_prefetch_desc(&maps.c);
-            mbar_expect_tx(&sh.q_full, chunks * kChunkBytes);
-            for (int c = 0; c < chunks; ++c) tma_load_4d(sQ + c * kChunkBytes, &maps.a, &sh.q_full, c * 64, q0, h, b);
+            if (me == 0) {
+                mbar_expect_tx(&sh.q_full, chunks * kChunkBytes);
+                for (int c = 0; c < chunks; ++c)
+                    tma_load_4d(sQ + c * kChunkBytes, &maps.a, &sh.q_full, c * 64, q0, h, b);
+            }
             int pos = 0;
             bool ok = true;
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (key_tile_state(p, b, h, j) == 0) continue;
                 // the K chunks of the tile, then the V chunks of this CTA's channel half
                 for (int i = 0; i < chunks + hc && ok; ++i, ++pos) {
+                    if ((pos & 1) != me) continue;
                     const int slot = pos % kRing, round = pos / kRing;
                     if (round > 0) ok = mbar_wait(&sh.empty[slot], (round - 1) & 1, abort_word, 10);
                     if (!ok) break;
