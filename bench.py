@@ -39,7 +39,7 @@ WORKLOADS = {
                       graph=True, published_tflops=214.7),
     "dit_masked": dict(B=2, Hq=24, Hkv=24, S=32768, D=128, dtype="bf16", causal=False, center_keys=False, seed=4,
                        masked_fraction=0.1),
-    # BASELINE config 4, second part: one long sequence sharded over the ranks (ring context parallelism).
+    # The video/DiT shape as ONE long sequence sharded over the ranks (ring context parallelism).
     # The sequence is divided by the number of ranks, so the job is fixed as N grows (strong scaling).
     "dit_ring": dict(B=1, Hq=24, Hkv=24, S=262144, D=128, dtype="bf16", causal=False, center_keys=False, seed=6,
                      masked_fraction=0.1, ring=True),

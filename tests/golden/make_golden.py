@@ -171,4 +171,4 @@ def main(reference_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("KFA_REFERENCE_CHECKOUT", "reference"))

@@ -436,7 +436,7 @@ def test_two_streams_give_identical_results():
 
 # --------------------------------------------------------- full-size properties
 def test_llm_gqa_config_row_sampled():
-    """BASELINE config 3 at batch 1: q scaled by 8, keys offset per head, tiny dO; checks sampled rows."""
+    """The default benchmark shape at batch 1: q scaled by 8, keys offset per head, tiny dO; checks sampled rows."""
     gen = torch.Generator().manual_seed(3)
     B, Hq, Hkv, S, D = 1, 8, 2, 4096, 128
     q = (8 * torch.randn(B, Hq, S, D, generator=gen)).bfloat16().cuda()
