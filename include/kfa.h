@@ -88,8 +88,10 @@ KFA_API int kfa_pack_mask(const kfa_tensor* mask, kfa_tensor* blocks, void* stre
 /* Bytes of scratch kfa_backward needs for these shapes (native.cpp:341-354 sizes the
  * same buffers: delta and its base).  For heads of 256, 384 or 512 channels the figure also
  * covers two 16-bit [B,Hq,Sq,ceil128(Sk)] matrices (rounded probabilities and score gradients)
- * that the wide-head tensor-core backward stores once and multiplies three times; when one
- * matrix would exceed 4 GiB they are left out and the general kernels run. */
+ * that the wide-head tensor-core backward stores once and multiplies three times.  Above 2 GiB
+ * per matrix (environment variable KFA_WIDE_MATRIX_BYTES overrides the limit) the backward runs in
+ * passes over batch elements and K/V-head groups that reuse one pass-sized pair of matrices; only
+ * when a single K/V head's group exceeds the limit are they left out and the general kernels run. */
 KFA_API size_t kfa_backward_workspace_bytes(const kfa_tensor* q, const kfa_tensor* k);
 
 /*

@@ -4,9 +4,11 @@
 #include "kfa_common.cuh"
 #include "launchers.h"
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -299,14 +301,76 @@ size_t delta_bytes(const kfa_tensor* q) {
     return ((rows * sizeof(float) + 255) / 256) * 256;
 }
 
-// Scratch of the wide-head backward behind the delta rows: the P_low and dS_low matrices.  Zero when
-// the head is not wide or the matrices would exceed 8 GiB (the general kernels run then).
-size_t wide_extra_bytes(const kfa_tensor* q, const kfa_tensor* k) {
-    if (!q || !k || q->ndim != 4 || k->ndim != 4) return 0;
+// Scratch of the wide-head backward behind the delta rows: the P_low and dS_low matrices of one pass.
+// A pass covers as many K/V heads (with their query heads) of one batch element as fit 2 GiB per matrix,
+// or the whole call when everything fits; zero when the head is not wide or a single K/V head's group
+// alone exceeds the limit (the general kernels run then).
+// KFA_WIDE_MATRIX_BYTES overrides the limit (a smaller value trades workspace for more passes).
+size_t wide_matrix_limit() {
+    if (const char* text = std::getenv("KFA_WIDE_MATRIX_BYTES")) {
+        const long long value = std::atoll(text);
+        if (value > 0) return (size_t)value;
+    }
+    return size_t(2) << 30;
+}
+
+struct WidePlan {
+    int heads_per_pass = 0;  // K/V heads per pass; 0 = not a wide-head call
+    bool single = false;     // one pass over the whole call (all batches)
+    size_t matrix_bytes = 0; // one stored matrix of a pass
+};
+
+WidePlan wide_plan(const kfa_tensor* q, const kfa_tensor* k) {
+    WidePlan plan;
+    if (!q || !k || q->ndim != 4 || k->ndim != 4) return plan;
     const int64_t D = q->sizes[3];
-    if (D != 256 && D != 384 && D != 512) return 0;
-    const size_t one = kfa::wide_stored_bytes(q->sizes[0], q->sizes[1], q->sizes[2], k->sizes[2]);
-    return one <= (size_t(4) << 30) ? 2 * one : 0;
+    if (D != 256 && D != 384 && D != 512) return plan;
+    const int64_t B = q->sizes[0], Hq = q->sizes[1], Hkv = k->sizes[1], Sq = q->sizes[2], Sk = k->sizes[2];
+    if (Hkv <= 0 || Hq % Hkv != 0) return plan;
+    const size_t kWideMatrixLimit = wide_matrix_limit();
+    const size_t all = kfa::wide_stored_bytes(B, Hq, Sq, Sk);
+    if (all <= kWideMatrixLimit) {
+        plan.heads_per_pass = (int)Hkv;
+        plan.single = true;
+        plan.matrix_bytes = all;
+        return plan;
+    }
+    const size_t one_group = kfa::wide_stored_bytes(1, Hq / Hkv, Sq, Sk);
+    if (one_group > kWideMatrixLimit) return plan;
+    plan.heads_per_pass = (int)std::min<int64_t>(Hkv, (int64_t)(kWideMatrixLimit / one_group));
+    plan.matrix_bytes = kfa::wide_stored_bytes(1, (Hq / Hkv) * plan.heads_per_pass, Sq, Sk);
+    return plan;
+}
+
+size_t wide_extra_bytes(const kfa_tensor* q, const kfa_tensor* k) { return 2 * wide_plan(q, k).matrix_bytes; }
+
+// The same call restricted to batch element b and K/V heads [h0, h0 + n).
+kfa::AttnParams wide_slice(const kfa::AttnParams& p, int b, int h0, int n) {
+    kfa::AttnParams s = p;
+    const int g = p.group, q0 = h0 * g;
+    auto shift = [](const void* base, int64_t elements) {
+        return static_cast<const void*>(static_cast<const char*>(base) + elements * 2);
+    };
+    s.q = shift(p.q, b * p.qs[0] + q0 * p.qs[1]);
+    s.k = shift(p.k, b * p.ks[0] + h0 * p.ks[1]);
+    s.v = shift(p.v, b * p.vs[0] + h0 * p.vs[1]);
+    s.out = const_cast<void*>(shift(p.out, b * p.os[0] + q0 * p.os[1]));
+    s.dout = shift(p.dout, b * p.gs[0] + q0 * p.gs[1]);
+    s.dq = const_cast<void*>(shift(p.dq, b * p.dqs[0] + q0 * p.dqs[1]));
+    s.dk = const_cast<void*>(shift(p.dk, b * p.dks[0] + h0 * p.dks[1]));
+    s.dv = const_cast<void*>(shift(p.dv, b * p.dvs[0] + h0 * p.dvs[1]));
+    const int64_t stat = ((int64_t)b * p.Hq + q0) * p.Sq;
+    s.maximum = p.maximum + stat;
+    s.logsum = p.logsum + stat;
+    s.delta = p.delta + stat;
+    if (p.has_mask) {
+        s.mask = p.mask + b * p.ms[0] + q0 * p.ms[1];
+        s.blocks = p.blocks + b * p.bs[0] + q0 * p.bs[1];
+    }
+    s.B = 1;
+    s.Hq = n * g;
+    s.Hkv = n;
+    return s;
 }
 
 }  // namespace
@@ -452,9 +516,23 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
         void* stored = static_cast<char*>(workspace) + delta_bytes(q);
         static const char* const names[5] = {"wide_scores_p", "wide_scores_ds", "wide_grad_q", "wide_grad_k",
                                              "wide_grad_v"};
-        for (int step = 0; step < 5; ++step) {
-            ce = timed(names[step], st, [&] { return kfa::launch_wide_backward(p, bf16, step, stored, st); });
-            if (ce != cudaSuccess) return cuda_fail(ce, "wide-head backward launch");
+        const WidePlan plan = wide_plan(q, k);
+        auto run_pass = [&](const kfa::AttnParams& pass) -> int {
+            for (int step = 0; step < 5; ++step) {
+                cudaError_t e = timed(names[step], st, [&] { return kfa::launch_wide_backward(pass, bf16, step, stored, st); });
+                if (e != cudaSuccess) return cuda_fail(e, "wide-head backward launch");
+            }
+            return 0;
+        };
+        if (plan.single) {
+            if (int e = run_pass(p)) return e;
+        } else {
+            // the stored matrices are reused pass by pass; passes are ordered on the stream
+            for (int b = 0; b < p.B; ++b)
+                for (int h0 = 0; h0 < p.Hkv; h0 += plan.heads_per_pass) {
+                    const int n = std::min(plan.heads_per_pass, p.Hkv - h0);
+                    if (int e = run_pass(wide_slice(p, b, h0, n))) return e;
+                }
         }
     } else {
         ce = timed("general_backward_q", st, [&] { return kfa::launch_general_backward(p, bf16, 0, st); });

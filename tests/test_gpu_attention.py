@@ -116,6 +116,24 @@ def test_wide_head_masks_and_scales(name, scale):
             assert float(grad.cpu()[hidden_keys[:, None, :].expand(B, Hkv, Sk)].abs().max()) == 0
 
 
+def test_wide_head_backward_in_head_group_passes(monkeypatch):
+    """With a small cap on the stored matrices the backward runs batch element by batch element and
+    K/V-head group by group over one reused workspace; results do not change."""
+    B, Hq, Hkv, S, D = 2, 4, 2, 300, 256
+    q, k, v, dout = make_inputs(B, Hq, Hkv, S, S, D, torch.bfloat16, seed=80)
+    whole = run_attention(api().attention, q, k, v, dout, causal=True)
+    one_group = 2 * S * 384 * 2  # two query heads x S rows x ceil128(S) columns x 2 bytes
+    monkeypatch.setenv("KFA_WIDE_MATRIX_BYTES", str(one_group + 256))
+    assert native().selected_family(q, k, v, None, True, backward=True) == 2
+    split = run_attention(api().attention, q, k, v, dout, causal=True)
+    for a, b in zip(whole, split):
+        assert torch.equal(a, b)
+    monkeypatch.setenv("KFA_WIDE_MATRIX_BYTES", str(one_group - 256))
+    assert native().selected_family(q, k, v, None, True, backward=True) == 0  # not even one group fits
+    monkeypatch.delenv("KFA_WIDE_MATRIX_BYTES")
+    check_against_oracle(split, q, k, v, dout, None, True, None)
+
+
 def test_wide_head_projection_layout():
     """[B, S, H, D] memory behind a [B, H, S, D] view is addressed through the tensor maps, no copy."""
     q, k, v, dout = make_inputs(1, 4, 2, 200, 200, 512, torch.bfloat16, seed=79)
