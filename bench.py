@@ -331,27 +331,55 @@ def main():
     kernels = native.profile_read(reset=True)
     status = native.device_status(reset=True)
 
-    # end to end from pinned host buffers, copies inside the timed region
+    # End to end from pinned host buffers, copies inside the timed region.  Every step uploads its own
+    # inputs and downloads its own results; like a training loop with a prefetching loader, the upload of
+    # step i+1 and the download of step i-1 run on side streams while step i computes (PCIe is full duplex),
+    # over two sets of device buffers.
     host_out = [torch.empty_like(t).pin_memory() for t in (hq, hq, hk, hv)]
+    compute = torch.cuda.current_stream()
+    up_stream, down_stream = torch.cuda.Stream(), torch.cuda.Stream()
+    dev_in = [[torch.empty_like(t, device=device) for t in (hq, hk, hv, hg)] for _ in range(2)]
+    dev_mask = [None if hmask is None else torch.empty_like(hmask, device=device) for _ in range(2)]
+    uploaded = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    downloaded = torch.cuda.Event()
 
-    def e2e_step():
-        q, k, v, g = (t.to(device, non_blocking=True) for t in (hq, hk, hv, hg))
-        m = None if hmask is None else hmask.to(device, non_blocking=True)
-        q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
-        results = step(q, k, v, g, m)
-        for dst, src in zip(host_out, results):
-            dst.copy_(src.detach(), non_blocking=True)
+    def e2e_run(count):
+        keep = []
+        for i in range(count):
+            slot = i % 2
+            with torch.cuda.stream(up_stream):
+                if i >= 2:
+                    up_stream.wait_event(consumed[slot])  # the step that last read this buffer set
+                for dst, src in zip(dev_in[slot], (hq, hk, hv, hg)):
+                    dst.copy_(src, non_blocking=True)
+                if hmask is not None:
+                    dev_mask[slot].copy_(hmask, non_blocking=True)
+                uploaded[slot].record(up_stream)
+            compute.wait_event(uploaded[slot])
+            q, k, v = (t.detach().requires_grad_(True) for t in dev_in[slot][:3])
+            results = step(q, k, v, dev_in[slot][3], dev_mask[slot])
+            consumed[slot].record(compute)
+            with torch.cuda.stream(down_stream):
+                down_stream.wait_event(consumed[slot])
+                if i >= 1:
+                    down_stream.wait_event(downloaded)  # host_out is reused step after step
+                for dst, src in zip(host_out, results):
+                    dst.copy_(src.detach(), non_blocking=True)
+                downloaded.record(down_stream)
+            keep.append(results)  # alive until the downloads have run
+        compute.wait_stream(down_stream)
+        return keep
 
-    for _ in range(2):
-        e2e_step()
+    e2e_run(2)
     barrier()
     b2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_steps = max(1, min(steps, 5))
+    e2e_steps = max(2, min(steps, 6))
     b2.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    held = e2e_run(e2e_steps)
     e2.record()
     barrier()
+    del held
     e2e_ms = b2.elapsed_time(e2)
 
     times = torch.tensor([elapsed_ms, e2e_ms], device=device, dtype=torch.float64)
@@ -409,7 +437,8 @@ def main():
             "frac_of_peak": {"burst": value / world / burst, "sustained": value / world / sustained if sustained else None,
                              "source": source},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / e2e_steps},
+                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
+                    "overlap": "uploads and downloads of neighbouring steps run on side streams during compute"},
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
             "device_status": status,
         }
