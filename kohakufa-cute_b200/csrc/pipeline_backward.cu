@@ -18,8 +18,11 @@ namespace {
 
 using namespace bwd;
 
-template <int D, bool BF16, bool KV>
+// MASKED = false is the instantiation for calls without a mask: the flag is cleared at compile time, so
+// none of the mask-table or mask-element code survives in it.
+template <int D, bool BF16, bool KV, bool MASKED>
 __global__ void __launch_bounds__(kThreads, 1) pipeline_backward(const __grid_constant__ Maps maps, AttnParams p) {
+    if (!MASKED) p.has_mask = 0;
     using C = Cfg<D>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -110,8 +113,8 @@ std::atomic<int> g_configured{0};
 template <int D, bool BF16, bool KV>
 cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
     using C = Cfg<D>;
-    cudaError_t e = cudaFuncSetAttribute(pipeline_backward<D, BF16, KV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::kSmemBytes);
+    auto kernel = p.has_mask ? pipeline_backward<D, BF16, KV, true> : pipeline_backward<D, BF16, KV, false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return e;
     constexpr int variant = (D == 128 ? 0 : 4) + (BF16 ? 0 : 2) + (KV ? 1 : 0);
     if (!(g_configured.load() & (1 << variant))) g_configured |= 1 << variant;
@@ -123,7 +126,7 @@ cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
     if (!encode_bhsd_map(&maps.g, p.dout, dt, p.D, p.Sq, p.Hq, p.B, p.gs, 64, kTile)) return cudaErrorInvalidValue;
     const int64_t tiles = KV ? (p.Sk + kTile - 1) / kTile : (p.Sq + kTile - 1) / kTile;
     const int64_t grid = tiles * p.B * (KV ? p.Hkv : p.Hq);
-    pipeline_backward<D, BF16, KV><<<(unsigned)grid, kThreads, C::kSmemBytes, st>>>(maps, p);
+    kernel<<<(unsigned)grid, kThreads, C::kSmemBytes, st>>>(maps, p);
     return cudaGetLastError();
 }
 
@@ -134,8 +137,6 @@ bool pipeline_backward_supported(const AttnParams& p, bool bf16) {
     if (p.D != 64 && p.D != 128) return false;
     if (p.nd != 0 || p.scale == 0.f) return false;
     if (p.Sk < 2) return false;  // a single key has P = 1: the general kernels keep dS exactly zero there
-    // only masks that are one key vector per batch (broadcast over heads and queries)
-    if (p.has_mask && (p.ms[2] != 0 || p.ms[1] != 0)) return false;
     if (!tma_compatible(p.q, p.qs, p.B, p.Hq, p.Sq) || !tma_compatible(p.k, p.ks, p.B, p.Hkv, p.Sk) ||
         !tma_compatible(p.v, p.vs, p.B, p.Hkv, p.Sk) || !tma_compatible(p.dout, p.gs, p.B, p.Hq, p.Sq))
         return false;

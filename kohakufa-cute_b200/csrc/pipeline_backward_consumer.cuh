@@ -28,9 +28,11 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
     // per-row quantities
     float row_m = INFINITY, row_ls = 0.f, row_dl = 0.f;
     bool row_ok = owner_row < owner_len;
-    const uint8_t* kmask = p.has_mask ? p.mask + (int64_t)w.b * p.ms[0] : nullptr;  // broadcast over heads, queries
+    // The mask element of (query head hq, query r, key c) is mask_b[hq*ms[1] + r*ms[2] + c*ms[3]].
+    const uint8_t* mask_b = p.has_mask ? p.mask + (int64_t)w.b * p.ms[0] : nullptr;
+    const bool key_padding = p.has_mask && p.ms[1] == 0 && p.ms[2] == 0;  // one line for all heads and queries
     if (KV) {
-        if (row_ok && kmask) row_ok = kmask[(int64_t)owner_row * p.ms[3]] != 0;
+        if (row_ok && key_padding) row_ok = mask_b[(int64_t)owner_row * p.ms[3]] != 0;
     } else if (row_ok) {
         const int64_t si = ((int64_t)w.b * p.Hq + w.head) * p.Sq + owner_row;
         row_m = p.maximum[si];
@@ -46,7 +48,22 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
     bool ok = true;
     while (w.valid(g) && ok) {
         if (KV) ok = mbar_wait(&sh.stats_full[unit & 1], (unit >> 1) & 1, abort_word, 140);
-        const int state = KV ? 2 : key_tile_state(p, w.b, w.head, i);
+        // key owners under key padding need no per-element test: a hidden key is a hidden owner row
+        const int state = (KV && (key_padding || !p.has_mask)) ? 2 : w.state(p, g, i);
+        // this thread's line of mask elements and the step between its columns
+        const uint8_t* mline = nullptr;
+        int64_t mstep = 0;
+        if (state == 1) {
+            const int64_t hq = w.query_head(g);
+            if (KV) {
+                mline = mask_b + hq * p.ms[1] + (int64_t)min(owner_row, p.Sk - 1) * p.ms[3];
+                mstep = p.ms[2];  // columns are queries
+            } else {
+                mline = mask_b + hq * p.ms[1] + (int64_t)min(owner_row, p.Sq - 1) * p.ms[2];
+                mstep = p.ms[3];  // columns are keys
+            }
+        }
+        const int col_last = (KV ? p.Sq : p.Sk) - 1;
         for (int sub = 0; sub < 2 && ok; ++sub) {
             KFA_TRACE_POINT(1, 1);
             ok = mbar_wait(&sh.sdp_ready[sub], unit & 1, abort_word, 141 + sub);
@@ -74,7 +91,7 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
             const float* st = s_stats + (unit & 1) * 3 * kTile + sub * kSub + wg * kCols;
 
             uint32_t pw[kCols / 2], dw[kCols / 2];
-            const bool masked = clip || (!KV && state == 1);
+            const bool masked = clip || state == 1;
             // One pair of columns: probabilities, their rounding, and the rounded score gradient.
             auto pair = [&](int c, bool apply_mask) {
                 float m0, m1, l0, l1, d0, d1;
@@ -98,9 +115,9 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<KV
                 if (apply_mask) {
                     pa = (c >= lo && c < hi) ? pa : 0.f;
                     pb = (c + 1 >= lo && c + 1 < hi) ? pb : 0.f;
-                    if (!KV && state == 1) {
-                        pa = kmask[(int64_t)min(col0 + c, p.Sk - 1) * p.ms[3]] != 0 ? pa : 0.f;
-                        pb = kmask[(int64_t)min(col0 + c + 1, p.Sk - 1) * p.ms[3]] != 0 ? pb : 0.f;
+                    if (state == 1) {
+                        pa = mline[(int64_t)min(col0 + c, col_last) * mstep] != 0 ? pa : 0.f;
+                        pb = mline[(int64_t)min(col0 + c + 1, col_last) * mstep] != 0 ? pb : 0.f;
                     }
                 }
                 const uint32_t packed = pack2<BF16>(pa, pb);

@@ -64,16 +64,20 @@ struct Shared {
     int abort_word;
 };
 
-// Combined state of a 128-key tile from the 64-key table entries: 0 hidden, 2 visible, 1 mixed.
-__device__ __forceinline__ int key_tile_state(const AttnParams& p, int b, int h, int j) {
+// Combined state of the 128 queries [q_lo, q_lo + 128) x 128 keys of tile j for query head h, from
+// the 64x64 table entries: 0 hidden, 2 visible, 1 mixed.  Collapsed (broadcast) axes of the table have
+// stride 0, so a mask broadcast over queries reads one row of entries.
+__device__ __forceinline__ int tile_state(const AttnParams& p, int b, int h, int q_lo, int j) {
     if (!p.has_mask) return 2;
     const int nk64 = (p.Sk + 63) >> 6;
     const int32_t* base = p.blocks + (int64_t)b * p.bs[0] + (int64_t)h * p.bs[1];
-    const int s0 = base[(int64_t)(2 * j) * p.bs[3]];
-    const int s1 = (2 * j + 1 < nk64) ? base[(int64_t)(2 * j + 1) * p.bs[3]] : s0;
-    if (s0 == 0 && s1 == 0) return 0;
-    if (s0 == 2 && s1 == 2) return 2;
-    return 1;
+    // two row blocks x two key blocks; the four loads are independent (one memory latency, not four)
+    const int64_t r0 = (int64_t)(q_lo >> 6) * p.bs[2];
+    const int64_t r1 = (int64_t)((min(q_lo + kTile, p.Sq) - 1) >> 6) * p.bs[2];
+    const int64_t c0 = (int64_t)(2 * j) * p.bs[3], c1 = (int64_t)min(2 * j + 1, nk64 - 1) * p.bs[3];
+    const int s00 = base[r0 + c0], s01 = base[r0 + c1], s10 = base[r1 + c0], s11 = base[r1 + c1];
+    if ((s00 | s01 | s10 | s11) == 0) return 0;
+    return (s00 & s01 & s10 & s11) == 2 ? 2 : 1;
 }
 
 // The CTA's place in the problem and its stream of work units.
@@ -82,6 +86,7 @@ struct Work {
     int b, head, owner0;  // batch, owner head (query head or K/V head), first owner row
     int first, end;       // streamed tile range [first, end)
     int groups;           // query heads per owner (KV) or 1
+    int fixed;            // state shared by every unit of this CTA (2 without a mask), or -1: look each unit up
 
     __device__ __forceinline__ void init(const AttnParams& p) {
         const int owner_len = KV ? p.Sk : p.Sq;
@@ -93,11 +98,16 @@ struct Work {
         head = (int)(bh % heads);
         b = (int)(bh / heads);
         owner0 = blk * kTile;
+        fixed = p.has_mask ? -1 : 2;
         if (KV) {
             groups = p.group;
             first = p.causal ? owner0 / kTile : 0;  // only queries r >= key see the key
             end = (p.Sq + kTile - 1) / kTile;
-            if (key_tile_state(p, b, head * p.group, blk) == 0) end = first;  // every key of the tile is hidden
+            // key padding (one line of mask for all queries and heads): a hidden key tile has no work at all
+            if (p.has_mask && p.bs[1] == 0 && p.bs[2] == 0) {
+                fixed = tile_state(p, b, 0, 0, blk);
+                if (fixed == 0) end = first;
+            }
         } else {
             groups = 1;
             first = 0;
@@ -106,24 +116,29 @@ struct Work {
             end = (k_hi + kTile - 1) / kTile;
         }
     }
-    // Unit cursor: (g, i).  Query owners skip key tiles the mask table marks hidden.
-    __device__ __forceinline__ bool live(const AttnParams& p, int i) const {
-        return KV || key_tile_state(p, b, head, i) != 0;
+    // Unit cursor: (g, i) = (query head of the group, streamed tile).  Units whose 128 x 128 block the mask
+    // table marks hidden are skipped; every role walks the same sequence.
+    __device__ __forceinline__ int state(const AttnParams& p, int g, int i) const {
+        if (fixed >= 0) return fixed;
+        return KV ? tile_state(p, b, head * groups + g, i * kTile, owner0 / kTile)
+                  : tile_state(p, b, head, owner0, i);
+    }
+    __device__ __forceinline__ void settle(const AttnParams& p, int& g, int& i) const {
+        while (g < groups) {
+            while (i < end && state(p, g, i) == 0) ++i;
+            if (i < end) return;
+            ++g;
+            i = first;
+        }
     }
     __device__ __forceinline__ void begin(const AttnParams& p, int& g, int& i) const {
-        g = 0;
+        g = first < end ? 0 : groups;
         i = first;
-        while (i < end && !live(p, i)) ++i;
-        if (i >= end) g = groups;
+        settle(p, g, i);
     }
     __device__ __forceinline__ void next(const AttnParams& p, int& g, int& i) const {
         ++i;
-        while (i < end && !live(p, i)) ++i;
-        if (i >= end) {
-            ++g;
-            i = first;
-            if (!KV) g = groups;
-        }
+        settle(p, g, i);
     }
     __device__ __forceinline__ bool valid(int g) const { return g < groups; }
     __device__ __forceinline__ int query_head(int g) const { return KV ? head * groups + g : head; }

@@ -36,13 +36,15 @@ constexpr int kTileQ = 128;
 constexpr int kTileK = 128;
 constexpr int kThreads = 384;  // three warpgroups: softmax 0, softmax 1, (MMA, loader, 2 idle warps)
 constexpr float kRebase = 8.0f;  // re-base the accumulator when the maximum grows by > 2^8
+constexpr int kMaxKeyTiles = 4096;  // masked calls keep one state byte per key tile in shared memory
 
 template <int D>
 struct FwdCfg {
     static constexpr int kChunks = D / 64;                 // 64-channel TMA boxes per tile
     static constexpr int kTileBytes = kTileK * D * 2;      // one Q, K or V tile
     static constexpr int kStages = D == 128 ? 4 : 6;       // K/V ring slots
-    static constexpr int kSmemBytes = 2 * kTileBytes + kStages * kTileBytes + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int kSmemBytes =
+        2 * kTileBytes + kStages * kTileBytes + 1024 /*align*/ + 256 /*barriers*/ + kMaxKeyTiles;
 };
 
 struct FwdMaps {
@@ -57,22 +59,35 @@ struct Shared {
     uint64_t p_ready[2];
     uint32_t tmem_base;
     int abort_word;
+    uint8_t tile_state[kMaxKeyTiles];  // per key tile of this CTA: 0 hidden, 1 mixed, 2 visible (masked calls)
 };
 
-// Combined state of key tile j (128 keys) from the 64-key table entries: 0 hidden, 2 visible, 1 mixed.
-__device__ __forceinline__ int key_tile_state(const AttnParams& p, int b, int h, int j) {
+// Combined state of key tile j (128 keys) for the CTA's query rows [q0, q0 + 256), from the 64x64
+// table entries: 0 hidden, 2 visible, 1 mixed.  Masks broadcast over queries have one row of entries.
+__device__ __forceinline__ int key_tile_state(const AttnParams& p, int b, int h, int q0, int j) {
     if (!p.has_mask) return 2;
     const int nk64 = (p.Sk + 63) >> 6;
     const int32_t* base = p.blocks + (int64_t)b * p.bs[0] + (int64_t)h * p.bs[1];
-    const int s0 = base[(int64_t)(2 * j) * p.bs[3]];
-    const int s1 = (2 * j + 1 < nk64) ? base[(int64_t)(2 * j + 1) * p.bs[3]] : s0;
-    if (s0 == 0 && s1 == 0) return 0;
-    if (s0 == 2 && s1 == 2) return 2;
-    return 1;
+    int r0 = 0, r1 = 0;
+    if (p.bs[2] != 0) {
+        r0 = q0 >> 6;
+        r1 = (min(q0 + 2 * kTileQ, p.Sq) - 1) >> 6;
+    }
+    const int c1 = min(2 * j + 1, nk64 - 1);
+    bool any = false, all = true;
+    for (int r = r0; r <= r1; ++r)
+        for (int c = 2 * j; c <= c1; ++c) {
+            const int s = base[(int64_t)r * p.bs[2] + (int64_t)c * p.bs[3]];
+            any = any || s != 0;
+            all = all && s == 2;
+        }
+    return all ? 2 : (any ? 1 : 0);
 }
 
-template <int D, bool BF16>
+// MASKED = false is the instantiation for calls without a mask (the flag is cleared at compile time).
+template <int D, bool BF16, bool MASKED>
 __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_constant__ FwdMaps maps, AttnParams p) {
+    if (!MASKED) p.has_mask = 0;
     using Cfg = FwdCfg<D>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -120,10 +135,15 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
         tmem_alloc(&sh.tmem_base, 512);
         tmem_relinquish();
     }
+    if (p.has_mask)
+        for (int j = threadIdx.x; j < n_max; j += kThreads) sh.tile_state[j] = (uint8_t)key_tile_state(p, b, h, q0, j);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh.tmem_base;
+    const uint8_t* states = sh.tile_state;
+    const bool masked_call = p.has_mask != 0;
+    auto state_of = [&](int j) -> int { return masked_call ? states[j] : 2; };
     volatile int* abort_word = &sh.abort_word;
 
     if (warp >= 8) {
@@ -144,7 +164,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
             int slot_use = 0;
             bool ok = true;
             for (int j = 0; j < n_max && ok; ++j) {
-                if (key_tile_state(p, b, h, j) == 0) continue;
+                if (state_of(j) == 0) continue;
                 for (int which = 0; which < 2 && ok; ++which) {  // K tile, then V tile
                     const int slot = slot_use % Cfg::kStages, round = slot_use / Cfg::kStages;
                     if (round > 0) ok = mbar_wait(&sh.kv_empty[slot], (round - 1) & 1, abort_word, 10);
@@ -189,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
             int slot_use = 0, iter[2] = {0, 0};
             // first visible key tile
             int j = 0;
-            while (j < n_max && key_tile_state(p, b, h, j) == 0) ++j;
+            while (j < n_max && state_of(j) == 0) ++j;
             if (ok && j < n_max) {
                 const int slot = slot_use % Cfg::kStages;
                 ok = mbar_wait(&sh.kv_full[slot], (slot_use / Cfg::kStages) & 1, abort_word, 21);
@@ -206,7 +226,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
             }
             while (ok && j < n_max) {
                 int jn = j + 1;
-                while (jn < n_max && key_tile_state(p, b, h, jn) == 0) ++jn;
+                while (jn < n_max && state_of(jn) == 0) ++jn;
                 const int v_slot = slot_use % Cfg::kStages, v_par = (slot_use / Cfg::kStages) & 1;
                 ++slot_use;
                 int k_slot = -1, k_par = 0;
@@ -256,12 +276,15 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
         const uint32_t s_addr = lane_base + t * 128, o_addr = lane_base + 256 + t * 128;
         const float c2 = fabsf(p.scale) * kLog2e;
         const uint64_t c2_pair = f2_pack(c2, c2);
-        const uint8_t* kmask = p.has_mask ? p.mask + (int64_t)b * p.ms[0] + (int64_t)h * p.ms[1] : nullptr;
+        // this row's line of the mask (every row shares one line when the mask is broadcast over queries)
+        const uint8_t* kmask = p.has_mask ? p.mask + (int64_t)b * p.ms[0] + (int64_t)h * p.ms[1] +
+                                                (int64_t)min(row, p.Sq - 1) * p.ms[2]
+                                          : nullptr;
         float m_used = -INFINITY, m_true = -INFINITY, l = 0.f;
         int iter = 0;
         bool ok = true;
         for (int j = 0; j < n_t[t] && ok; ++j) {
-            const int state = key_tile_state(p, b, h, j);
+            const int state = state_of(j);
             if (state == 0) continue;
             KFA_TRACE_POINT(1 + t, 1);
             ok = mbar_wait(&sh.s_ready[t], iter & 1, abort_word, 30 + t);
@@ -411,8 +434,8 @@ template <int D, bool BF16>
 cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
     using Cfg = FwdCfg<D>;
     // The shared-memory opt-in is per device; it is cheap, so it is simply repeated per call.
-    cudaError_t e = cudaFuncSetAttribute(pipeline_forward<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kSmemBytes);
+    auto kernel = p.has_mask ? pipeline_forward<D, BF16, true> : pipeline_forward<D, BF16, false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     constexpr int variant = (D == 128 ? 0 : 2) + (BF16 ? 0 : 1);
     const int bit = 1 << variant;
@@ -423,7 +446,7 @@ cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
     if (!encode_bhsd_map(&maps.k, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kTileK)) return cudaErrorInvalidValue;
     if (!encode_bhsd_map(&maps.v, p.v, dt, p.D, p.Sk, p.Hkv, p.B, p.vs, 64, kTileK)) return cudaErrorInvalidValue;
     const int64_t grid = (int64_t)((p.Sq + 2 * kTileQ - 1) / (2 * kTileQ)) * p.B * p.Hq;
-    pipeline_forward<D, BF16><<<(unsigned)grid, kThreads, Cfg::kSmemBytes, st>>>(maps, p);
+    kernel<<<(unsigned)grid, kThreads, Cfg::kSmemBytes, st>>>(maps, p);
     return cudaGetLastError();
 }
 
@@ -434,7 +457,7 @@ bool pipeline_forward_supported(const AttnParams& p, bool bf16) {
     if (p.D != 64 && p.D != 128) return false;
     if (p.nd != 0) return false;
     if (p.scale == 0.f || p.Sk < 2) return false;  // hidden scores are -inf; -inf * 0 is not representable in the fast path
-    if (p.has_mask && p.ms[2] != 0) return false;  // only masks broadcast over the query axis
+    if (p.has_mask && (p.Sk + kTileK - 1) / kTileK > kMaxKeyTiles) return false;
     if (!tma_compatible(p.q, p.qs, p.B, p.Hq, p.Sq) || !tma_compatible(p.k, p.ks, p.B, p.Hkv, p.Sk) ||
         !tma_compatible(p.v, p.vs, p.B, p.Hkv, p.Sk))
         return false;

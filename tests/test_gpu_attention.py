@@ -196,6 +196,11 @@ def test_boolean_masks(name, causal, D):
     gen = torch.Generator().manual_seed(31)
     mask = _mask_variants(B, Hq, Sq, Sk, gen)[name].cuda()
     q, k, v, dout = make_inputs(B, Hq, Hkv, Sq, Sk, D, torch.bfloat16, seed=32)
+    if D in (64, 128):
+        # every mask shape, full per-head 4-D masks included, runs on the tensor-memory kernels
+        expanded = mask.expand(B, Hq, Sq, Sk)
+        assert native().selected_family(q, k, v, expanded, causal) == 1
+        assert native().selected_family(q, k, v, expanded, causal, backward=True) == 1
     actual = run_attention(api().attention, q, k, v, dout, mask=mask, causal=causal)
     _, contract = check_against_oracle(actual, q, k, v, dout, mask, causal, None)
     # all-hidden rows give exactly zero output and zero dQ
@@ -204,6 +209,20 @@ def test_boolean_masks(name, causal, D):
     if bool(hidden.any()):
         assert float(actual[0].cpu()[hidden].abs().max()) == 0
         assert float(actual[1].cpu()[hidden].abs().max()) == 0
+
+
+def test_block_sparse_full_mask_long_sequence():
+    """A full [Sq, Sk] mask with hidden, mixed and visible 128x128 blocks (a banded document mask with ragged
+    edges) at a length where tile skipping matters; per-head variation through a second, shifted band."""
+    B, H, S, D = 1, 2, 1536, 128
+    q, k, v, dout = make_inputs(B, H, H, S, S, D, torch.bfloat16, seed=6)
+    idx = torch.arange(S)
+    band0 = (idx[:, None] // 200 == idx[None, :] // 200)           # documents of 200 tokens
+    band1 = ((idx[:, None] - idx[None, :]).abs() < 333)            # a sliding band
+    mask = torch.stack([band0, band1])[None].cuda()                # [1, H, S, S]
+    assert native().selected_family(q, k, v, mask, True) == 1
+    actual = run_attention(api().attention, q, k, v, dout, mask=mask, causal=True)
+    check_against_oracle(actual, q, k, v, dout, mask, True, None)
 
 
 def test_key_padding_long_sequence_skips_hidden_tiles():
