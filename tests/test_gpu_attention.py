@@ -448,6 +448,58 @@ def test_cuda_graph_replay_with_changed_inputs_and_mask():
         torch.testing.assert_close(got, ref, atol=0, rtol=0)
 
 
+@pytest.mark.parametrize("kind", ("wide_head", "neighborhood"))
+def test_cuda_graph_replay_of_the_other_tensor_core_families(kind):
+    """Forward + backward of the wide-head and neighbourhood families captured once and replayed on new data."""
+    K = api()
+    gen = torch.Generator().manual_seed(84)
+    if kind == "wide_head":
+        shape_q, shape_k, dtype = (1, 4, 200, 512), (1, 2, 200, 512), torch.bfloat16
+
+        def call(q, k, v):
+            return K.attention(q, k, v, causal=True)
+    else:
+        shape_q = shape_k = (1, 2, 4 * 10 * 12, 64)
+        dtype = torch.float16
+
+        def call(q, k, v):
+            return K.neighborhood_attention(q, k, v, spatial_shape=(4, 10, 12), window_size=(3, 5, 7), scale=0.125)
+
+    def fresh():
+        q = torch.randn(shape_q, generator=gen).to(dtype).cuda()
+        k = torch.randn(shape_k, generator=gen).to(dtype).cuda()
+        v = torch.randn(shape_k, generator=gen).to(dtype).cuda()
+        g = torch.randn(shape_q, generator=gen).to(dtype).cuda()
+        return q, k, v, g
+
+    q, k, v, dout = fresh()
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            torch.autograd.grad(call(*leaves), leaves, dout)
+    torch.cuda.current_stream().wait_stream(stream)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        out = call(*leaves)
+        grads = torch.autograd.grad(out, leaves, dout)
+    q2, k2, v2, dout2 = fresh()
+    with torch.no_grad():
+        for leaf, new in zip(leaves, (q2, k2, v2)):
+            leaf.copy_(new)
+        dout.copy_(dout2)
+        out.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    again = [t.detach().clone().requires_grad_(True) for t in leaves]
+    ref_out = call(*again)
+    ref = (ref_out.detach(), *torch.autograd.grad(ref_out, again, dout))
+    for got, want in zip((out, *grads), ref):
+        torch.testing.assert_close(got, want, atol=0, rtol=0)
+    assert native().device_status(reset=True) == 0
+
+
 def test_two_streams_give_identical_results():
     import threading
 
