@@ -176,23 +176,28 @@ def measured_peaks():
     return 1590.0, 1400.0, 6650.0, "fallback"
 
 
-def cpu_oracle_sample(w, repeats=1):
-    """Times the CPU oracle (the reference's PyTorch path restated) on one (batch, query-head) unit."""
+def cpu_oracle_sample(w, budget_seconds=10.0):
+    """Times the CPU oracle (the reference's PyTorch path restated) on (batch, query-head) units of the
+    workload, one after another with fresh seeded data, until about ``budget_seconds`` of CPU work is done."""
     from oracle import attention_oracle as ao
 
     dtype = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
     S = min(w["S"], 4096)
     D = w["D"]
     gen = torch.Generator().manual_seed(w["seed"])
-    q, k, v, g = (torch.randn(1, 1, S, D, generator=gen).to(dtype) for _ in range(4))
     causal = w["causal"]
-    ao.contract_reference((q[:, :, :256], k[:, :, :256], v[:, :, :256]), g[:, :, :256], None, causal, None)  # warm
-    begin = time.perf_counter()
-    for _ in range(repeats):
+    warm = [torch.randn(1, 1, 256, D, generator=gen).to(dtype) for _ in range(4)]
+    ao.contract_reference(tuple(warm[:3]), warm[3], None, causal, None)
+    units, seconds = 0, 0.0
+    while units < 2 or (seconds < budget_seconds and units < 4096):
+        q, k, v, g = (torch.randn(1, 1, S, D, generator=gen).to(dtype) for _ in range(4))
+        begin = time.perf_counter()
         ao.contract_reference((q, k, v), g, None, causal, None)
-    seconds = (time.perf_counter() - begin) / repeats
-    flops = 3.5 * 4 * D * (S * S / 2 if causal else S * S)
-    return flops / seconds / 1e12, seconds, f"1 (batch, query head) unit: S={S}, D={D}, causal={causal}, {w['dtype']}"
+        seconds += time.perf_counter() - begin
+        units += 1
+    flops = units * 3.5 * 4 * D * (S * S / 2 if causal else S * S)
+    return (flops / seconds / 1e12, seconds,
+            f"{units} (batch, query head) units: S={S}, D={D}, causal={causal}, {w['dtype']}")
 
 
 def reference_arm(args, w, rank):
@@ -200,8 +205,9 @@ def reference_arm(args, w, rank):
         return
     steps, warmup = max(1, args.steps), max(0, args.warmup)
     for _ in range(min(warmup, 1)):
-        cpu_oracle_sample(w)
-    values = [cpu_oracle_sample(w) for _ in range(min(steps, 5))]
+        cpu_oracle_sample(w, 1.0)
+    # each step is a bounded sample (about three seconds of host work) of the same workload
+    values = [cpu_oracle_sample(w, 3.0) for _ in range(min(steps, 20))]
     value = statistics.mean(x[0] for x in values)
     seconds = statistics.mean(x[1] for x in values)
     line = {
