@@ -45,6 +45,10 @@ WORKLOADS = {
                      masked_fraction=0.1, ring=True),
     "dit_ring_small": dict(B=1, Hq=24, Hkv=24, S=65536, D=128, dtype="bf16", causal=False, center_keys=False, seed=6,
                            masked_fraction=0.1, ring=True),
+    # the reference's published 2-D neighbourhood shape on B200: 151.28 us forward+backward (CUDA-graph median)
+    "neighborhood_2d": dict(B=1, Hq=8, Hkv=8, S=64 * 64, D=64, dtype="bf16", causal=False, center_keys=False,
+                            seed=7, grid=(64, 64), window=(7, 7), graph=True,
+                            published_tflops=3.5 * 4 * 8 * 64 * 4096 * 49 / 151.28e-6 / 1e12),
     "neighborhood_3d": dict(B=1, Hq=16, Hkv=16, S=16 * 32 * 32, D=64, dtype="fp16", causal=False, center_keys=False,
                             seed=5, grid=(16, 32, 32), window=(3, 7, 7)),
 }
