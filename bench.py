@@ -37,6 +37,11 @@ WORKLOADS = {
     "llm_gqa_small": dict(B=2, Hq=16, Hkv=4, S=4096, D=128, dtype="bf16", causal=True, center_keys=True, seed=3),
     "wide_head": dict(B=1, Hq=16, Hkv=16, S=1024, D=512, dtype="bf16", causal=True, center_keys=False, seed=21,
                       graph=True, published_tflops=214.7),
+    # further shapes the reference publishes for B200 (its own kernels: 70 and 138 TFLOP/s fwd+bwd)
+    "wide_head_4k": dict(B=1, Hq=16, Hkv=16, S=4096, D=512, dtype="bf16", causal=True, center_keys=False, seed=22,
+                         published_tflops=70.0),
+    "d128_4k": dict(B=1, Hq=16, Hkv=16, S=4096, D=128, dtype="bf16", causal=True, center_keys=False, seed=23,
+                    graph=True, published_tflops=138.0),
     "dit_masked": dict(B=2, Hq=24, Hkv=24, S=32768, D=128, dtype="bf16", causal=False, center_keys=False, seed=4,
                        masked_fraction=0.1),
     # The video/DiT shape as ONE long sequence sharded over the ranks (ring context parallelism).
