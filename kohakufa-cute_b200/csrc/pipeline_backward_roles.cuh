@@ -92,9 +92,14 @@ struct Work {
         const int owner_len = KV ? p.Sk : p.Sq;
         const int heads = KV ? p.Hkv : p.Hq;
         const int nblk = (owner_len + kTile - 1) / kTile;
-        int blk = (int)(blockIdx.x % nblk);
-        if (!KV) blk = nblk - 1 - blk;  // causal: late query tiles carry the most work, start them first
-        const int64_t bh = blockIdx.x / nblk;
+        // Heavy tiles first (late query tiles, early key tiles under a causal mask).  Large grids go head by
+        // head; grids of a few waves go tile row by tile row over all heads, so that no head's heavy tiles
+        // start in the last wave.
+        const int64_t nbh = (int64_t)p.B * heads;
+        const bool by_row = (int64_t)gridDim.x < 4 * 148;
+        int blk = (int)(by_row ? blockIdx.x / nbh : blockIdx.x % nblk);
+        if (!KV) blk = nblk - 1 - blk;
+        const int64_t bh = by_row ? blockIdx.x % nbh : blockIdx.x / nblk;
         head = (int)(bh % heads);
         b = (int)(bh / heads);
         owner0 = blk * kTile;

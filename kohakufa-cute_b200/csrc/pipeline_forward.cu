@@ -97,8 +97,13 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nblk = (p.Sq + 2 * kTileQ - 1) / (2 * kTileQ);
-    const int qblk = nblk - 1 - (int)(blockIdx.x % nblk);  // heavy (late) causal blocks first
-    const int64_t bh = blockIdx.x / nblk;
+    // Heavy (late) causal blocks first.  Large grids go head by head (a head's CTAs share K/V in L2 and the
+    // last wave is made of light blocks); grids of a few waves go block-row by block-row over all heads, so
+    // that no head's heavy blocks start in the last wave.
+    const int64_t nbh = (int64_t)p.B * p.Hq;
+    const bool by_row = (int64_t)gridDim.x < 4 * 148;
+    const int qblk = nblk - 1 - (int)(by_row ? blockIdx.x / nbh : blockIdx.x % nblk);
+    const int64_t bh = by_row ? blockIdx.x % nbh : blockIdx.x / nblk;
     const int h = (int)(bh % p.Hq), b = (int)(bh / p.Hq);
     const int kvh = h / p.group;
     const int q0 = qblk * 2 * kTileQ;
