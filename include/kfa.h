@@ -183,6 +183,16 @@ KFA_API void kfa_profile_reset(void);
  */
 KFA_API int kfa_device_status(int reset);
 
+/*
+ * Self-test of the failure-detection chain (no counterpart in the reference): launches `ctas` CTAs
+ * that each wait at most `limit_cycles` SM cycles on a barrier that nothing completes.  No fault is
+ * raised: the waits run out, the first CTAs report code 9001 through kfa_device_status() and set the
+ * launch-wide abort flag; CTAs that start afterwards skip their wait (their number is returned in
+ * `skipped`, which may be null).  Until kfa_device_status(1) clears the condition, every tensor-memory
+ * kernel of this library skips its work as well.  Synchronises the stream.
+ */
+KFA_API int kfa_self_test_wait(long long limit_cycles, int ctas, int* skipped, void* stream);
+
 /* Which kernel family kfa_forward / kfa_backward would select for these operands:
  * 0 = general kernels, 1 = tcgen05 tensor-memory pipeline (heads of 64/128 channels),
  * 2 = tcgen05 wide-head kernels (256/384/512 channels).  (The reference exposes its

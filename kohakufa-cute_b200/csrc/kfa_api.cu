@@ -65,6 +65,7 @@ cudaError_t timed(const char* name, cudaStream_t st, F&& launch) {
 constexpr int kMaxDevices = 64;
 int* g_status_host[kMaxDevices] = {};
 int* g_status_dev[kMaxDevices] = {};
+int* g_abort_dev[kMaxDevices] = {};  // device memory: launch-wide abort flag (see AttnParams::abort_flag)
 std::mutex g_status_mutex;
 
 int* status_word(int* err) {
@@ -89,10 +90,25 @@ int* status_word(int* err) {
             *err = cuda_fail(e, "cudaHostGetDevicePointer(status)");
             return nullptr;
         }
+        int* flag = nullptr;
+        e = cudaMalloc(reinterpret_cast<void**>(&flag), 256);
+        if (e == cudaSuccess) e = cudaMemset(flag, 0, 256);
+        if (e != cudaSuccess) {
+            *err = cuda_fail(e, "cudaMalloc(abort flag)");
+            return nullptr;
+        }
         g_status_host[dev] = host;
         g_status_dev[dev] = devp;
+        g_abort_dev[dev] = flag;
     }
     return g_status_dev[dev];
+}
+
+int* abort_flag_of_current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    return g_abort_dev[dev];
 }
 
 bool is_half_type(const kfa_tensor* t) { return t->dtype == KFA_F16 || t->dtype == KFA_BF16; }
@@ -162,6 +178,7 @@ int fill_common(kfa::AttnParams& p, const kfa_tensor* q, const kfa_tensor* k, co
     }
     int err = 0;
     p.status = status_word(&err);
+    p.abort_flag = abort_flag_of_current_device();
     return err;
 }
 
@@ -247,8 +264,34 @@ int kfa_device_status(int reset) {
     std::lock_guard<std::mutex> lock(g_status_mutex);
     if (!g_status_host[dev]) return 0;
     const int value = *reinterpret_cast<volatile int*>(g_status_host[dev]);
-    if (reset) *reinterpret_cast<volatile int*>(g_status_host[dev]) = 0;
+    if (reset) {
+        *reinterpret_cast<volatile int*>(g_status_host[dev]) = 0;
+        // after a reported failure the abort flag keeps every later CTA idle until it is cleared here
+        if (value != 0 && g_abort_dev[dev]) cudaMemset(g_abort_dev[dev], 0, 256);
+    }
     return value;
+}
+
+int kfa_self_test_wait(long long limit_cycles, int ctas, int* skipped_out, void* stream) {
+    if (limit_cycles <= 0 || limit_cycles > 2000000000LL || ctas <= 0 || ctas > 65535)
+        return fail(KFA_INVALID_ARGUMENT, "self test: limit must be 1..2e9 cycles and ctas 1..65535");
+    int err = 0;
+    int* status = status_word(&err);
+    if (!status) return err;
+    int* flag = abort_flag_of_current_device();
+    int* counter = nullptr;
+    cudaError_t ce = cudaMalloc(reinterpret_cast<void**>(&counter), sizeof(int));
+    if (ce != cudaSuccess) return cuda_fail(ce, "self test allocation");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaMemsetAsync(counter, 0, sizeof(int), st);
+    ce = kfa::launch_wait_probe(status, flag, limit_cycles, ctas, counter, st);
+    int skipped = 0;
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(&skipped, counter, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(st);
+    cudaFree(counter);
+    if (ce != cudaSuccess) return cuda_fail(ce, "self test launch");
+    if (skipped_out) *skipped_out = skipped;
+    return 0;
 }
 
 void kfa_profile_enable(int on) {

@@ -39,7 +39,8 @@ struct AttnParams {
     int ext[3];
     int win[3];
     int two_term;
-    int* status;  // device-visible status word (mapped host memory)
+    int* status;      // device-visible status word (mapped host memory)
+    int* abort_flag;  // device memory: set by the first CTA whose bounded wait gives up; later CTAs skip their work
 };
 
 template <typename T>

@@ -41,6 +41,9 @@ cudaError_t launch_na_pipeline_forward(const AttnParams& p, bool bf16, cudaStrea
 bool na_pipeline_backward_supported(const AttnParams& p);
 cudaError_t launch_na_pipeline_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st);
 
+// Failure-detection self-test: CTAs wait `limit` cycles on a barrier nothing completes.
+cudaError_t launch_wait_probe(int* status, int* abort_flag, long long limit, int ctas, int* skipped, cudaStream_t st);
+
 int pipeline_configured_variants();
 void pipeline_forget_variants();
 

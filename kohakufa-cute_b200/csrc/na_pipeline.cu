@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
     const int q0 = qblk * kTile;
 
     if (threadIdx.x == 0) {
-        sh.abort_word = 0;
+        sh.abort_word = *reinterpret_cast<volatile int*>(p.abort_flag) != 0 ? 90 : 0;  // 90: an earlier CTA gave up
         mbar_init(&sh.q_full, 1);
         for (int i = 0; i < kRing; ++i) {
             mbar_init(&sh.full[i], 1);
@@ -97,7 +97,9 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
     const uint32_t tmem = sh.tmem_base;
     volatile int* abort_word = &sh.abort_word;
 
-    if (warp == 5) {
+    if (sh.abort_word != 0) {
+        // an earlier CTA gave up: skip straight to the tear-down
+    } else if (warp == 5) {
         if (lane == 0) {
             tma_prefetch_desc(&maps.q);
             tma_prefetch_desc(&maps.k);
@@ -307,7 +309,10 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 4000 + sh.abort_word;
+    if (threadIdx.x == 0 && sh.abort_word != 0 && sh.abort_word != 90) {  // 90 = skipped: already reported
+        *p.status = 4000 + sh.abort_word;
+        *reinterpret_cast<volatile int*>(p.abort_flag) = 1;  // the remaining CTAs of this and later launches skip their work
+    }
     if (warp == 4) tmem_dealloc(tmem, 256);
 }
 
@@ -357,7 +362,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
     const int owner0 = blk * kTile;
 
     if (threadIdx.x == 0) {
-        sh.abort_word = 0;
+        sh.abort_word = *reinterpret_cast<volatile int*>(p.abort_flag) != 0 ? 90 : 0;  // 90: an earlier CTA gave up
         mbar_init(&sh.own_full, 1);
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&sh.full[i], 1);
@@ -387,7 +392,9 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
     const uint32_t tmem = sh.tmem_base;
     volatile int* abort_word = &sh.abort_word;
 
-    if (warp == 5) {
+    if (sh.abort_word != 0) {
+        // an earlier CTA gave up: skip straight to the tear-down
+    } else if (warp == 5) {
         if (lane == 0) {
             tma_prefetch_desc(&maps.own0);
             tma_prefetch_desc(&maps.own1);
@@ -611,7 +618,10 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 4100 + sh.abort_word;
+    if (threadIdx.x == 0 && sh.abort_word != 0 && sh.abort_word != 90) {  // 90 = skipped: already reported
+        *p.status = 4100 + sh.abort_word;
+        *reinterpret_cast<volatile int*>(p.abort_flag) = 1;  // the remaining CTAs of this and later launches skip their work
+    }
     if (warp == 4) tmem_dealloc(tmem, 256);
 }
 

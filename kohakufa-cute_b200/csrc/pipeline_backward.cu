@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward(const __grid_co
     w.init(p);
 
     if (threadIdx.x == 0) {
-        sh.abort_word = 0;
+        sh.abort_word = *reinterpret_cast<volatile int*>(p.abort_flag) != 0 ? 90 : 0;  // 90: an earlier CTA gave up
         mbar_init(&sh.owner_full, 1);
         for (int s = 0; s < C::kPairs; ++s) {
             mbar_init(&sh.pair_full[s], 1);
@@ -59,10 +59,12 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward(const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh.tmem_base;
+    const bool dead = sh.abort_word != 0;  // set before the barrier above: skip straight to the tear-down
 
     // With two consumer warpgroups (384 threads, 168 registers at launch) registers move from the role
     // warpgroup to the consumers; with four (640 threads, 96 registers) every role fits as launched.
-    if (warp >= kRoleWarp) {
+    if (dead) {
+    } else if (warp >= kRoleWarp) {
         if (kGroups == 2) reg_dealloc<96>();
         if (warp <= kRoleWarp + 1) {
             if (lane == 0) mma_role<D, BF16, KV>(p, w, sh, tmem, s_owner, s_ring, warp - kRoleWarp);
@@ -77,7 +79,10 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward(const __grid_co
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 2000 + sh.abort_word;
+    if (threadIdx.x == 0 && sh.abort_word != 0 && sh.abort_word != 90) {  // 90 = skipped: already reported
+        *p.status = 2000 + sh.abort_word;
+        *reinterpret_cast<volatile int*>(p.abort_flag) = 1;  // the remaining CTAs of this and later launches skip their work
+    }
     if (warp == kRoleWarp) tmem_dealloc(tmem, 512);
 }
 

@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
     const int n_max = max(n_t[0], n_t[1]);
 
     if (threadIdx.x == 0) {
-        sh.abort_word = 0;
+        sh.abort_word = *reinterpret_cast<volatile int*>(p.abort_flag) != 0 ? 90 : 0;  // 90: an earlier CTA gave up
         mbar_init(&sh.q_full, 1);
         for (int i = 0; i < Cfg::kStages; ++i) {
             mbar_init(&sh.kv_full[i], 1);
@@ -151,7 +151,9 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
     auto state_of = [&](int j) -> int { return masked_call ? states[j] : 2; };
     volatile int* abort_word = &sh.abort_word;
 
-    if (warp >= 8) {
+    const bool dead = sh.abort_word != 0;  // set before the barrier above: skip straight to the tear-down
+    if (dead) {
+    } else if (warp >= 8) {
       reg_dealloc<88>();
       if (warp == 9) {
         // ------------------------------------------------------------ loader
@@ -429,7 +431,10 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 1000 + sh.abort_word;
+    if (threadIdx.x == 0 && sh.abort_word != 0 && sh.abort_word != 90) {  // 90 = skipped: already reported
+        *p.status = 1000 + sh.abort_word;
+        *reinterpret_cast<volatile int*>(p.abort_flag) = 1;  // the remaining CTAs of this and later launches skip their work
+    }
     if (warp == 8) tmem_dealloc(tmem, 512);
 }
 

@@ -72,9 +72,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // pipelines pay on every tile.
 constexpr long long kWaitCycles = 4000000000LL;
 
-// Waits for the phase with the given parity. Returns false when the CTA has
-// been aborted (by this wait running out, or by another role).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word, int where) {
+// Waits for the phase with the given parity, for at most `limit` cycles.  Returns false when the CTA
+// has been aborted (by this wait running out, or by another role).
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_word, int where,
+                                                long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     for (;;) {
@@ -82,10 +83,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_word != 0) return false;
-        if (clock64() - start > kWaitCycles) break;
+        if (clock64() - start > limit) break;
     }
     *abort_word = where;
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word, int where) {
+    return mbar_wait_limit(bar, parity, abort_word, where, kWaitCycles);
 }
 
 // ---------------------------------------------------------------------- TMA

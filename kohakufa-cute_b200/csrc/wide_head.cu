@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
     const int n_tiles = key_tiles_of(p, q0);
 
     if (threadIdx.x == 0) {
-        sh.abort_word = 0;
+        sh.abort_word = *reinterpret_cast<volatile int*>(p.abort_flag) != 0 ? 90 : 0;  // 90: an earlier CTA gave up
         mbar_init(&sh.q_full, 1);
         for (int i = 0; i < kRing; ++i) {
             mbar_init(&sh.full[i], 1);
@@ -123,7 +123,9 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
     const uint32_t tmem = sh.tmem_base;
     volatile int* abort_word = &sh.abort_word;
 
-    if (warp == 5 || warp == 7) {
+    if (sh.abort_word != 0) {
+        // an earlier CTA gave up: skip straight to the tear-down
+    } else if (warp == 5 || warp == 7) {
         // --------------------------------------------------------------- loaders
         // Two loading threads take alternate ring positions: one thread's stream of 16 KB boxes does not
         // keep the ring full.
@@ -360,7 +362,10 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 3000 + sh.abort_word;
+    if (threadIdx.x == 0 && sh.abort_word != 0 && sh.abort_word != 90) {  // 90 = skipped: already reported
+        *p.status = 3000 + sh.abort_word;
+        *reinterpret_cast<volatile int*>(p.abort_flag) = 1;  // the remaining CTAs of this and later launches skip their work
+    }
     if (warp == 4) tmem_dealloc(tmem, 512);
 }
 
@@ -410,7 +415,7 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
     const int n_tiles = key_tiles_of(p, q0);
 
     if (threadIdx.x == 0) {
-        sh.abort_word = 0;
+        sh.abort_word = *reinterpret_cast<volatile int*>(p.abort_flag) != 0 ? 90 : 0;  // 90: an earlier CTA gave up
         mbar_init(&sh.own_full, 1);
         for (int i = 0; i < kRing; ++i) {
             mbar_init(&sh.full[i], 1);
@@ -432,7 +437,9 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
     const uint32_t tmem = sh.tmem_base;
     volatile int* abort_word = &sh.abort_word;
 
-    if (warp == 5) {
+    if (sh.abort_word != 0) {
+        // an earlier CTA gave up: skip straight to the tear-down
+    } else if (warp == 5) {
         if (lane == 0) {
             tma_prefetch_desc(&maps.a);
             tma_prefetch_desc(&maps.b);
@@ -575,7 +582,10 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 3100 + sh.abort_word;
+    if (threadIdx.x == 0 && sh.abort_word != 0 && sh.abort_word != 90) {  // 90 = skipped: already reported
+        *p.status = 3100 + sh.abort_word;
+        *reinterpret_cast<volatile int*>(p.abort_flag) = 1;  // the remaining CTAs of this and later launches skip their work
+    }
     if (warp == 4) tmem_dealloc(tmem, 512);
 }
 
@@ -628,7 +638,7 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Wide
     const int units = per_pass * passes;
 
     if (threadIdx.x == 0) {
-        sh.abort_word = 0;
+        sh.abort_word = *reinterpret_cast<volatile int*>(p.abort_flag) != 0 ? 90 : 0;  // 90: an earlier CTA gave up
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh.full[i], 1);
             mbar_init(&sh.empty[i], 1);
@@ -646,7 +656,9 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Wide
     const uint32_t tmem = sh.tmem_base;
     volatile int* abort_word = &sh.abort_word;
 
-    if (warp == 5) {
+    if (sh.abort_word != 0) {
+        // an earlier CTA gave up: skip straight to the tear-down
+    } else if (warp == 5) {
         if (lane == 0 && units > 0) {
             tma_prefetch_desc(&maps.a);
             tma_prefetch_desc(&maps.b);
@@ -726,7 +738,10 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Wide
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && sh.abort_word != 0) *p.status = 3200 + sh.abort_word;
+    if (threadIdx.x == 0 && sh.abort_word != 0 && sh.abort_word != 90) {  // 90 = skipped: already reported
+        *p.status = 3200 + sh.abort_word;
+        *reinterpret_cast<volatile int*>(p.abort_flag) = 1;  // the remaining CTAs of this and later launches skip their work
+    }
     if (warp == 4) tmem_dealloc(tmem, 256);
 }
 

@@ -71,6 +71,8 @@ SIGNATURES = {
                                          ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_uint64)]),
     "kfa_profile_reset": (None, []),
     "kfa_selected_family": (ctypes.c_int, [_TP, _TP, _TP, _TP, ctypes.c_int, ctypes.c_int]),
+    "kfa_self_test_wait": (ctypes.c_int, [ctypes.c_longlong, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+                                          ctypes.c_void_p]),
 }
 
 _lock = threading.Lock()
@@ -270,6 +272,17 @@ def merge_partial(acc_out, acc_maximum, acc_logsum, part_out, part_maximum, part
     with torch.cuda.device(acc_out.device):
         records = [describe(t) for t in (acc_out, acc_maximum, acc_logsum, part_out, part_maximum, part_logsum)]
         _check(lib.kfa_merge_partial(*[_ref(r) for r in records], float(scale), _stream(acc_out.device)))
+
+
+def self_test_wait(limit_cycles, ctas, device=None):
+    """Runs the failure-detection self-test (``kfa_self_test_wait``); returns the number of CTAs that
+    skipped their wait because an earlier one had already given up."""
+    lib = library()
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    skipped = ctypes.c_int(0)
+    with torch.cuda.device(device):
+        _check(lib.kfa_self_test_wait(int(limit_cycles), int(ctas), ctypes.byref(skipped), _stream(device)))
+    return skipped.value
 
 
 def selected_family(q, k, v, mask=None, causal=False, backward=False):
