@@ -418,8 +418,7 @@ def main():
             # algorithmic GEMMs (of 7) attributed per kernel: forward 2; the dQ kernel 1 (dQ) + half of the shared
             # S/dP pair; the dK/dV kernel 2 (dK, dV) + the other half; every wide-head backward kernel forms one
             share = {"pipeline_forward": 2.0, "general_forward": 2.0, "neighborhood_forward": 2.0, "na_pipeline_forward": 2.0, "wide_forward": 2.0,
-                     "wide_scores_p": 1.0, "wide_scores_ds": 1.0, "wide_grad_q": 1.0, "wide_grad_k": 1.0,
-                     "wide_grad_v": 1.0}.get(name)
+                     "wide_scores_p": 1.0, "wide_scores_ds": 1.0, "wide_grad": 3.0}.get(name)
             if share is None:
                 share = 1.5 if name.endswith("_q") else 3.5
             prof_steps = 3 if use_graph else steps

@@ -557,11 +557,10 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
         if (ce != cudaSuccess) return cuda_fail(ce, "pipeline backward (dK/dV) launch");
     } else if (wide) {
         void* stored = static_cast<char*>(workspace) + delta_bytes(q);
-        static const char* const names[5] = {"wide_scores_p", "wide_scores_ds", "wide_grad_q", "wide_grad_k",
-                                             "wide_grad_v"};
+        static const char* const names[3] = {"wide_scores_p", "wide_scores_ds", "wide_grad"};
         const WidePlan plan = wide_plan(q, k);
         auto run_pass = [&](const kfa::AttnParams& pass) -> int {
-            for (int step = 0; step < 5; ++step) {
+            for (int step = 0; step < 3; ++step) {
                 cudaError_t e = timed(names[step], st, [&] { return kfa::launch_wide_backward(pass, bf16, step, stored, st); });
                 if (e != cudaSuccess) return cuda_fail(e, "wide-head backward launch");
             }

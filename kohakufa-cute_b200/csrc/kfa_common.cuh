@@ -6,6 +6,11 @@
 #include <stdint.h>
 #include <math.h>
 
+// Grids below this many CTAs are ordered tile row by tile row over all heads (see the pipeline kernels).
+#ifndef KFA_ROW_MAJOR_LIMIT
+#define KFA_ROW_MAJOR_LIMIT (4 * 148)
+#endif
+
 namespace kfa {
 
 constexpr float kLog2e = 1.4426950408889634f;

@@ -96,7 +96,7 @@ struct Work {
         // head; grids of a few waves go tile row by tile row over all heads, so that no head's heavy tiles
         // start in the last wave.
         const int64_t nbh = (int64_t)p.B * heads;
-        const bool by_row = (int64_t)gridDim.x < 4 * 148;
+        const bool by_row = (int64_t)gridDim.x < KFA_ROW_MAJOR_LIMIT;
         int blk = (int)(by_row ? blockIdx.x / nbh : blockIdx.x % nblk);
         if (!KV) blk = nblk - 1 - blk;
         const int64_t bh = by_row ? blockIdx.x % nbh : blockIdx.x / nblk;

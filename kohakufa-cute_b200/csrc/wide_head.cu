@@ -598,25 +598,36 @@ struct GradShared {
     int abort_word;
 };
 
-// WHICH 0: dQ[q tile] = scale * sum_kt dS_low[q tile, kt] K[kt]        (A K-major,  rows = queries)
-// WHICH 1: dK[k tile] = scale * sum_{g,i} dS_low[i, k tile]^T Q_g[i]   (A MN-major, rows = keys)
-// WHICH 2: dV[k tile] =         sum_{g,i} P_low[i, k tile]^T dO_g[i]
-// maps.a = the stored matrix, maps.b = K, Q or dO.  A CTA owns 128 output rows and one half of the
-// channels.  192 threads: warps 0-3 epilogue (thread <-> output row), warp 4 MMA issuer, warp 5
+struct GradMaps {
+    CUtensorMap ds, p, k, q, g;  // the two stored matrices, K, Q and dO
+};
+
+// One launch forms all three gradients; the block index selects the product:
+//   0: dQ[q tile] = scale * sum_kt dS_low[q tile, kt] K[kt]        (A K-major,  rows = queries)
+//   1: dK[k tile] = scale * sum_{g,i} dS_low[i, k tile]^T Q_g[i]   (A MN-major, rows = keys)
+//   2: dV[k tile] =         sum_{g,i} P_low[i, k tile]^T dO_g[i]
+// (first `n_dq` blocks dQ, then `n_kv` blocks dK, then `n_kv` blocks dV; inside a product heavy causal
+// tiles of all heads come first, so the launch ends on light dV tiles.)  A CTA owns 128 output rows and
+// one half of the channels.  192 threads: warps 0-3 epilogue (thread <-> output row), warp 4 MMA issuer, warp 5
 // loader.  A stage holds one 128 x 128 block of the matrix (2 chunks) and 128 rows x D/2 channels
 // of the other operand.
-template <int WHICH, bool BF16>
-__global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ WideMaps maps, AttnParams p) {
+template <bool BF16>
+__global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ GradMaps maps, AttnParams p, unsigned n_dq,
+                                                    unsigned n_kv) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    constexpr bool KV = WHICH != 0;
+    const int which = blockIdx.x < n_dq ? 0 : (blockIdx.x < n_dq + n_kv ? 1 : 2);
+    const unsigned local = blockIdx.x - (which == 0 ? 0u : (which == 1 ? n_dq : n_dq + n_kv));
+    const bool KV = which != 0;
+    const CUtensorMap* map_a = which == 2 ? &maps.p : &maps.ds;
+    const CUtensorMap* map_b = which == 0 ? &maps.k : (which == 1 ? &maps.q : &maps.g);
     const int hc = p.D >> 7;
     const int stage_bytes = (2 + hc) * kChunkBytes;
     GradShared& sh = *reinterpret_cast<GradShared*>(smem + 2 * stage_bytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int half = blockIdx.x & 1;
-    const int64_t rest = blockIdx.x >> 1;
+    const int half = local & 1;
+    const int64_t rest = local >> 1;
     const int owner_len = KV ? p.Sk : p.Sq, heads = KV ? p.Hkv : p.Hq;
     const int nblk = (owner_len + kTile - 1) / kTile;
     const int64_t nbh = (int64_t)p.B * heads;
@@ -660,8 +671,8 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Wide
         // an earlier CTA gave up: skip straight to the tear-down
     } else if (warp == 5) {
         if (lane == 0 && units > 0) {
-            tma_prefetch_desc(&maps.a);
-            tma_prefetch_desc(&maps.b);
+            tma_prefetch_desc(map_a);
+            tma_prefetch_desc(map_b);
             bool ok = true;
             for (int u = 0; u < units && ok; ++u) {
                 const int g = u / per_pass, i = first + u % per_pass;
@@ -673,11 +684,11 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Wide
                 const int hq = KV ? head * p.group + g : head;
                 const int q_row = KV ? i * kTile : owner0, k_col = KV ? owner0 : i * kTile;
                 for (int c = 0; c < 2; ++c)
-                    tma_load_4d(dst + c * kChunkBytes, &maps.a, &sh.full[s], k_col + c * 64, q_row, hq, b);
+                    tma_load_4d(dst + c * kChunkBytes, map_a, &sh.full[s], k_col + c * 64, q_row, hq, b);
                 // the other operand: K rows of the key tile (dQ), Q / dO rows of the query tile (dK / dV)
                 const int b_row = i * kTile, b_head = KV ? hq : head / p.group;
                 for (int c = 0; c < hc; ++c)
-                    tma_load_4d(dst + (2 + c) * kChunkBytes, &maps.b, &sh.full[s], (half * hc + c) * 64, b_row, b_head,
+                    tma_load_4d(dst + (2 + c) * kChunkBytes, map_b, &sh.full[s], (half * hc + c) * 64, b_row, b_head,
                                 b);
             }
         }
@@ -707,11 +718,11 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Wide
         using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
         const int row = owner0 + warp * 32 + lane;
         const int width = 64 * hc;
-        void* base = WHICH == 0 ? p.dq : WHICH == 1 ? p.dk : p.dv;
-        const int64_t* os = WHICH == 0 ? p.dqs : WHICH == 1 ? p.dks : p.dvs;
+        void* base = which == 0 ? p.dq : which == 1 ? p.dk : p.dv;
+        const int64_t* os = which == 0 ? p.dqs : which == 1 ? p.dks : p.dvs;
         T* out = reinterpret_cast<T*>(base) + (int64_t)b * os[0] + (int64_t)head * os[1] + (int64_t)row * os[2] +
                  half * width;
-        const float mul = WHICH == 2 ? 1.f : p.scale;
+        const float mul = which == 2 ? 1.f : p.scale;
         if (units == 0) {
             if (row < owner_len)
                 for (int d = 0; d < width; d += 8) *reinterpret_cast<uint4*>(out + d) = make_uint4(0, 0, 0, 0);
@@ -830,22 +841,22 @@ cudaError_t scores_t(const AttnParams& p, const Stored& stored, cudaStream_t st)
     return cudaGetLastError();
 }
 
-template <int WHICH, bool BF16>
+template <bool BF16>
 cudaError_t grad_t(const AttnParams& p, const Stored& stored, cudaStream_t st) {
     const int bytes = smem_grad(p.D);
-    cudaError_t e = opt_in(wide_grad<WHICH, BF16>, bytes);
+    cudaError_t e = opt_in(wide_grad<BF16>, bytes);
     if (e != cudaSuccess) return e;
-    WideMaps maps;
+    GradMaps maps;
     const CUtensorMapDataType dt = map_type(BF16);
-    bool ok = encode_stored(&maps.a, WHICH == 2 ? stored.p_low : stored.ds_low, BF16, p, stored.pitch);
-    if (WHICH == 0) ok = ok && encode_bhsd_map(&maps.b, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kTile);
-    if (WHICH == 1) ok = ok && encode_bhsd_map(&maps.b, p.q, dt, p.D, p.Sq, p.Hq, p.B, p.qs, 64, kTile);
-    if (WHICH == 2) ok = ok && encode_bhsd_map(&maps.b, p.dout, dt, p.D, p.Sq, p.Hq, p.B, p.gs, 64, kTile);
+    const bool ok = encode_stored(&maps.ds, stored.ds_low, BF16, p, stored.pitch) &&
+                    encode_stored(&maps.p, stored.p_low, BF16, p, stored.pitch) &&
+                    encode_bhsd_map(&maps.k, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kTile) &&
+                    encode_bhsd_map(&maps.q, p.q, dt, p.D, p.Sq, p.Hq, p.B, p.qs, 64, kTile) &&
+                    encode_bhsd_map(&maps.g, p.dout, dt, p.D, p.Sq, p.Hq, p.B, p.gs, 64, kTile);
     if (!ok) return cudaErrorInvalidValue;
-    maps.c = maps.a;
-    const int owner_len = WHICH == 0 ? p.Sq : p.Sk, heads = WHICH == 0 ? p.Hq : p.Hkv;
-    const int64_t grid = (int64_t)((owner_len + kTile - 1) / kTile) * p.B * heads * 2;
-    wide_grad<WHICH, BF16><<<(unsigned)grid, 192, bytes, st>>>(maps, p);
+    const int64_t n_dq = (int64_t)((p.Sq + kTile - 1) / kTile) * p.B * p.Hq * 2;
+    const int64_t n_kv = (int64_t)((p.Sk + kTile - 1) / kTile) * p.B * p.Hkv * 2;
+    wide_grad<BF16><<<(unsigned)(n_dq + 2 * n_kv), 192, bytes, st>>>(maps, p, (unsigned)n_dq, (unsigned)n_kv);
     return cudaGetLastError();
 }
 
@@ -878,7 +889,7 @@ cudaError_t launch_wide_delta(const AttnParams& p, bool bf16, cudaStream_t st) {
     return cudaGetLastError();
 }
 
-// step 0: P_low, 1: dS_low, 2: dQ, 3: dK, 4: dV.  `stored` holds the two matrices back to back.
+// step 0: P_low, 1: dS_low, 2: dQ, dK and dV in one launch.  `stored` holds the two matrices back to back.
 cudaError_t launch_wide_backward(const AttnParams& p, bool bf16, int step, void* stored, cudaStream_t st) {
     Stored s;
     s.pitch = (p.Sk + kTile - 1) / kTile * kTile;
@@ -889,9 +900,7 @@ cudaError_t launch_wide_backward(const AttnParams& p, bool bf16, int step, void*
     switch (step) {
         case 0: return bf16 ? scores_t<0, true>(p, s, st) : scores_t<0, false>(p, s, st);
         case 1: return bf16 ? scores_t<1, true>(p, s, st) : scores_t<1, false>(p, s, st);
-        case 2: return bf16 ? grad_t<0, true>(p, s, st) : grad_t<0, false>(p, s, st);
-        case 3: return bf16 ? grad_t<1, true>(p, s, st) : grad_t<1, false>(p, s, st);
-        default: return bf16 ? grad_t<2, true>(p, s, st) : grad_t<2, false>(p, s, st);
+        default: return bf16 ? grad_t<true>(p, s, st) : grad_t<false>(p, s, st);
     }
 }
 
