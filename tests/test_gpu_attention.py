@@ -500,6 +500,30 @@ def test_cuda_graph_replay_of_the_other_tensor_core_families(kind):
     assert native().device_status(reset=True) == 0
 
 
+def test_activation_checkpointing_and_prescaled_queries():
+    """The caller patterns of the reference's integration notes: a [B, S, H, D] projection layout, queries
+    that already carry the softmax scale (scale = 1.0), and recomputation under torch.utils.checkpoint."""
+    from torch.utils.checkpoint import checkpoint
+
+    K = api()
+    q, k, v, dout = make_inputs(2, 4, 2, 384, 384, 128, torch.bfloat16, seed=85)
+    q = (q.float() * 128 ** -0.5).to(torch.bfloat16)
+    q, k, v = (strided_like_projection(t) for t in (q, k, v))
+
+    def block(q_, k_, v_):
+        return K.attention(q_, k_, v_, causal=True, scale=1.0)
+
+    plain = [t.detach().clone().requires_grad_(True) for t in (q, k, v)]
+    out_plain = block(*plain)
+    grads_plain = torch.autograd.grad(out_plain, plain, dout)
+    again = [t.detach().clone().requires_grad_(True) for t in (q, k, v)]
+    out_ckpt = checkpoint(block, *again, use_reentrant=False)
+    grads_ckpt = torch.autograd.grad(out_ckpt, again, dout)
+    for a, b in zip((out_plain, *grads_plain), (out_ckpt, *grads_ckpt)):
+        torch.testing.assert_close(a, b, atol=0, rtol=0)
+    check_against_oracle((out_plain.detach(), *grads_plain), q, k, v, dout, None, True, 1.0)
+
+
 def test_two_streams_give_identical_results():
     import threading
 
