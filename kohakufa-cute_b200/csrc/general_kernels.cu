@@ -623,6 +623,9 @@ cudaError_t launch_general_backward(const AttnParams& p, bool bf16, int which, c
 // workspace: kMeanSplits * B*H*D partial sums followed by B*H*D means
 cudaError_t launch_center_keys(const void* k, void* out, float* workspace, bool bf16, int B, int H, int S, int D,
                                const int64_t* ks, const int64_t* os, cudaStream_t st) {
+    // one launch over thread-block clusters when a head's slab fits in shared memory
+    if (center_keys_cluster_supported(k, out, S, D, ks, os))
+        return launch_center_keys_cluster(k, out, bf16, B, H, S, D, ks, os, st);
     const int splits = max(1, min(kMeanSplits, S / 128));
     float* partial = workspace;
     float* mean = workspace + (int64_t)kMeanSplits * B * H * D;

@@ -607,7 +607,10 @@ int kfa_center_keys(const kfa_tensor* k, kfa_tensor* centered, void* workspace, 
                                        k->strides, centered->strides, st);
     });
     if (ce != cudaSuccess) return cuda_fail(ce, "center_keys launch");
-    g_launches += 2;  // three kernels per call
+    // the one-launch cluster kernel, or three kernels (partial sums, means, subtraction)
+    if (!kfa::center_keys_cluster_supported(k->data, centered->data, (int)k->sizes[2], (int)k->sizes[3], k->strides,
+                                            centered->strides))
+        g_launches += 2;
     return 0;
 }
 

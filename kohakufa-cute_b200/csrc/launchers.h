@@ -11,6 +11,9 @@ cudaError_t launch_output_delta(const AttnParams& p, bool bf16, cudaStream_t st)
 cudaError_t launch_general_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st);
 cudaError_t launch_center_keys(const void* k, void* out, float* mean, bool bf16, int B, int H, int S, int D,
                                const int64_t* ks, const int64_t* os, cudaStream_t st);
+bool center_keys_cluster_supported(const void* k, const void* out, int S, int D, const int64_t* ks, const int64_t* os);
+cudaError_t launch_center_keys_cluster(const void* k, void* out, bool bf16, int B, int H, int S, int D,
+                                       const int64_t* ks, const int64_t* os, cudaStream_t st);
 cudaError_t launch_merge_partial(float* acc, float* am, float* al, const void* part, const float* pm, const float* pl,
                                  bool bf16, int B, int H, int S, int D, const int64_t* ps, float scale,
                                  cudaStream_t st);

@@ -381,6 +381,37 @@ def test_center_keys_kernel_matches_the_contract(dtype):
     assert float(back.float().sum(-2).abs().max()) < 0.1
 
 
+@pytest.mark.parametrize("shape", ((4, 8, 4096, 128), (1, 3, 1000, 64), (2, 2, 65, 512), (1, 2, 777, 256)))
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
+def test_center_keys_cluster_kernel(shape, dtype):
+    """Heads whose slab fits in shared memory are centred by one launch over thread-block clusters: same
+    values as the FP32 definition (to one rounding of the mean), bitwise reproducible, any 16-byte row layout."""
+    B, H, S, D = shape
+    gen = torch.Generator().manual_seed(S + D)
+    k = (torch.randn(B, H, S, D, generator=gen) + 3 * torch.randn(B, H, 1, D, generator=gen)).to(dtype).cuda()
+    _, names = _launched(lambda: native().center_keys(k))
+    assert names == {"center_keys"}
+    got = native().center_keys(k)
+    want = (k.float() - k.float().mean(dim=2, keepdim=True)).to(dtype)
+    ulp = 2 ** (-7 if dtype == torch.bfloat16 else -10)
+    assert float((got.float() - want.float()).abs().max()) <= float(want.float().abs().max()) * ulp
+    torch.testing.assert_close(native().center_keys(k), got, atol=0, rtol=0)
+    strided = strided_like_projection(k)
+    torch.testing.assert_close(native().center_keys(strided), got, atol=0, rtol=0)
+    assert float(got.float().sum(2).abs().max()) < 0.02 * S ** 0.5 * float(want.float().abs().max()) + 0.1
+
+
+def _launched(fn):
+    native().profile_read(reset=True)
+    native().profile_enable(True)
+    try:
+        result = fn()
+        torch.cuda.synchronize()
+    finally:
+        native().profile_enable(False)
+    return result, set(native().profile_read(reset=True))
+
+
 @pytest.mark.parametrize("causal,masked", ((False, False), (True, False), (False, True), (True, True)))
 def test_centered_attention_matches_fp64(causal, masked):
     gen = torch.Generator().manual_seed(44)
