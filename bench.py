@@ -316,7 +316,6 @@ def main():
             step(dq_, dk_, dv_, dg_, dmask)
 
     native.profile_read(reset=True)
-    native.profile_enable(not use_graph)
     sampler = ClockSampler(local_rank)
     sampler.start()
     time.sleep(0.3)
@@ -333,16 +332,18 @@ def main():
     elapsed_ms = begin_evt.elapsed_time(end_evt)
     launches = launches_per_step * steps if use_graph else native.launch_count() - launches_before
     clocks = sampler.stop(wall_begin, wall_end)
-    native.profile_enable(False)
-    if use_graph:
-        # Per-kernel CUDA events cannot sit inside a captured graph: time the same kernels in a short eager pass
-        # whose launches are queued behind a device-side delay, so that host launch gaps stay out of the events.
-        native.profile_enable(True)
-        for _ in range(3):
+    # Per-kernel times come from a profiled pass right after the timed region: with per-kernel events on, the
+    # library launches its kernels one after another on one stream (in the timed region the two backward
+    # owners overlap on two streams, and a captured graph cannot hold the events at all).  For short steps the
+    # launches are queued behind a device-side delay, so that host launch gaps stay out of the events.
+    prof_steps = 3 if use_graph else steps
+    native.profile_enable(True)
+    for _ in range(prof_steps):
+        if use_graph:
             torch.cuda._sleep(4_000_000)
-            step(dq_, dk_, dv_, dg_, dmask)
-        barrier()
-        native.profile_enable(False)
+        step(dq_, dk_, dv_, dg_, dmask)
+    barrier()
+    native.profile_enable(False)
     kernels = native.profile_read(reset=True)
     status = native.device_status(reset=True)
 
@@ -421,13 +422,13 @@ def main():
                      "wide_scores_p": 1.0, "wide_scores_ds": 1.0, "wide_grad": 3.0}.get(name)
             if share is None:
                 share = 1.5 if name.endswith("_q") else 3.5
-            prof_steps = 3 if use_graph else steps
             per_step = max(1, int(round(count / prof_steps)))  # a ring step launches each kernel once per block
             per_launch = flops / (world if w.get("ring") else 1) * share / 7.0 / per_step
             achieved = per_launch / (total_ms / count * 1e-3) / 1e12
             peak = sustained or burst
             roofline = {"bound": "tensor", "kernel": name, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                         "frac": achieved / peak, "traffic": None, "peak_source": f"{source} (sustained bf16 GEMM)",
+                        "timing": f"CUDA events of a profiled pass of {prof_steps} steps after the timed region, kernels serialised",
                         "kernel_ms": total_ms / count,
                         "all_kernels_ms": {k: v[0] / v[1] for k, v in kernels.items()}}
         cpu = None

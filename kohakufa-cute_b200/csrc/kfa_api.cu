@@ -60,6 +60,38 @@ cudaError_t timed(const char* name, cudaStream_t st, F&& launch) {
     return e;
 }
 
+// A side stream with its fork/join events per caller stream (created on first use, kept for the process).
+struct Side {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+std::mutex g_side_mutex;
+std::vector<std::pair<std::pair<int, cudaStream_t>, Side*>> g_sides;
+
+Side* side_stream_for(cudaStream_t user) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    std::lock_guard<std::mutex> lock(g_side_mutex);
+    for (auto& entry : g_sides)
+        if (entry.first.first == dev && entry.first.second == user) return entry.second;
+    // creating a stream is not allowed while the caller's stream is being captured: stay on one stream then
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(user, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    Side* side = new Side;
+    if (cudaStreamCreateWithFlags(&side->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&side->fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&side->join, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        delete side;
+        return nullptr;
+    }
+    g_sides.push_back({{dev, user}, side});
+    return side;
+}
+
 // Per-device status word in mapped host memory: kernels write it only when a
 // bounded wait gives up; the host reads it without synchronising.
 constexpr int kMaxDevices = 64;
@@ -551,10 +583,25 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
     });
     if (ce != cudaSuccess) return cuda_fail(ce, "output_delta launch");
     if (pipeline) {
-        ce = timed("pipeline_backward_q", st, [&] { return kfa::launch_pipeline_backward(p, bf16, 0, st); });
-        if (ce != cudaSuccess) return cuda_fail(ce, "pipeline backward (dQ) launch");
-        ce = timed("pipeline_backward_kv", st, [&] { return kfa::launch_pipeline_backward(p, bf16, 1, st); });
+        // The two gradient owners depend on delta only, not on each other: the key owners go to a side
+        // stream so that the query owners' CTAs fill the SMs the first grid frees while it drains.
+        // (Not while per-kernel timing is on: an event pair must bracket one kernel alone.)
+        Side* side = g_profile_on.load(std::memory_order_relaxed) ? nullptr : side_stream_for(st);
+        cudaStream_t kv_stream = st;
+        if (side && cudaEventRecord(side->fork, st) == cudaSuccess &&
+            cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess)
+            kv_stream = side->stream;
+        ce = timed("pipeline_backward_kv", kv_stream,
+                   [&] { return kfa::launch_pipeline_backward(p, bf16, 1, kv_stream); });
+        cudaError_t cq = timed("pipeline_backward_q", st, [&] { return kfa::launch_pipeline_backward(p, bf16, 0, st); });
+        if (kv_stream != st) {
+            // always join, also after a failed launch: the caller's stream must not lose the side stream
+            cudaError_t cj = cudaEventRecord(side->join, kv_stream);
+            if (cj == cudaSuccess) cj = cudaStreamWaitEvent(st, side->join, 0);
+            if (ce == cudaSuccess) ce = cj;
+        }
         if (ce != cudaSuccess) return cuda_fail(ce, "pipeline backward (dK/dV) launch");
+        if (cq != cudaSuccess) return cuda_fail(cq, "pipeline backward (dQ) launch");
     } else if (wide) {
         void* stored = static_cast<char*>(workspace) + delta_bytes(q);
         static const char* const names[3] = {"wide_scores_p", "wide_scores_ds", "wide_grad"};
