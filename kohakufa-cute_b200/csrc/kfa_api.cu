@@ -577,11 +577,28 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
     const bool bf16 = q->dtype == KFA_BF16;
     const bool pipeline = kfa::pipeline_backward_supported(p, bf16);
     const bool wide = !pipeline && kfa::wide_backward_supported(p) && wide_extra_bytes(q, k) > 0;
-    cudaError_t ce = timed("output_delta", st, [&] {
-        if (wide) return kfa::launch_wide_delta(p, bf16, st);
+    // Wide heads: the first score kernel (P_low) needs only the forward's statistics, so delta runs on a side
+    // stream beside it and joins before the second score kernel.  (Serial while per-kernel timing is on.)
+    Side* delta_side = (wide && !g_profile_on.load(std::memory_order_relaxed)) ? side_stream_for(st) : nullptr;
+    cudaStream_t delta_stream = st;
+    if (delta_side && cudaEventRecord(delta_side->fork, st) == cudaSuccess &&
+        cudaStreamWaitEvent(delta_side->stream, delta_side->fork, 0) == cudaSuccess)
+        delta_stream = delta_side->stream;
+    cudaError_t ce = timed("output_delta", delta_stream, [&] {
+        if (wide) return kfa::launch_wide_delta(p, bf16, delta_stream);
         return pipeline ? kfa::launch_pipeline_delta(p, bf16, st) : kfa::launch_output_delta(p, bf16, st);
     });
-    if (ce != cudaSuccess) return cuda_fail(ce, "output_delta launch");
+    bool delta_joined = delta_stream == st;
+    auto join_delta = [&]() -> cudaError_t {
+        if (delta_joined) return cudaSuccess;
+        delta_joined = true;
+        cudaError_t e = cudaEventRecord(delta_side->join, delta_stream);
+        return e == cudaSuccess ? cudaStreamWaitEvent(st, delta_side->join, 0) : e;
+    };
+    if (ce != cudaSuccess) {
+        join_delta();
+        return cuda_fail(ce, "output_delta launch");
+    }
     if (pipeline) {
         // The two gradient owners depend on delta only, not on each other: the key owners go to a side
         // stream so that the query owners' CTAs fill the SMs the first grid frees while it drains.
@@ -609,7 +626,11 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
         auto run_pass = [&](const kfa::AttnParams& pass) -> int {
             for (int step = 0; step < 3; ++step) {
                 cudaError_t e = timed(names[step], st, [&] { return kfa::launch_wide_backward(pass, bf16, step, stored, st); });
-                if (e != cudaSuccess) return cuda_fail(e, "wide-head backward launch");
+                if (e == cudaSuccess && step == 0) e = join_delta();  // dS_low needs delta
+                if (e != cudaSuccess) {
+                    join_delta();
+                    return cuda_fail(e, "wide-head backward launch");
+                }
             }
             return 0;
         };
