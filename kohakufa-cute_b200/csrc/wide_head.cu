@@ -72,7 +72,7 @@ struct FwdShared {
 };
 
 // maps.a = Q, maps.b = K, maps.c = V.  256 threads: warps 0-3 softmax (thread <-> query row),
-// warps 4 and 6 MMA issuers, warp 5 loader.  A tcgen05.mma holds its issuing thread for about a
+// warps 4 and 6 MMA issuers, warps 5 and 7 loaders.  A tcgen05.mma holds its issuing thread for about a
 // hundred cycles whatever its size, and a 512-channel score tile needs 32 of them, so the scores are
 // formed by TWO issuers into two partial accumulators: issuer 0 contracts the even 64-channel chunks
 // into S_a (column 0), issuer 1 the odd ones into S_b (column 128); the softmax adds the two.  Each
