@@ -171,3 +171,44 @@ def test_tensor_core_family_matches_window_enumeration_at_full_size(spatial, win
         # two roundings to the 16-bit type of (almost) the same FP32 value differ by at most one ulp
         assert ao.per_head_relative_error(a.cpu(), b.cpu().double()) < 0.5 * TOL[dtype]["norm"], name
         torch.testing.assert_close(a.float(), b.float(), atol=TOL[dtype]["elem"], rtol=TOL[dtype]["elem"])
+
+
+def _random_geometry(index):
+    gen = torch.Generator().manual_seed(7000 + index)
+
+    def rand(lo, hi):
+        return int(torch.randint(lo, hi + 1, (1,), generator=gen))
+
+    nd = 2 if index % 3 == 0 else 3
+    while True:
+        spatial = tuple(rand(1, 14 if nd == 3 else 40) for _ in range(nd))
+        tokens = 1
+        for n in spatial:
+            tokens *= n
+        if 2 <= tokens <= 1600:
+            break
+    while True:
+        window = tuple(rand(1, min(n, 11)) for n in spatial)
+        seen = 1
+        for w in window:
+            seen *= w
+        if seen >= 2:  # a window of one key has P = 1 and zero score gradients: nothing to compare relatively
+            break
+    dtype = torch.float16 if index % 2 else torch.bfloat16
+    scale = (0.125, -0.125, 0.3)[index % 3]
+    return spatial, window, dtype, scale, tokens
+
+
+@pytest.mark.parametrize("index", range(24))
+def test_random_grids_and_windows(index):
+    """Seeded random grids and windows (windows equal to the extent, windows of one, extents of one, odd sizes)
+    through the tensor-core family, against the oracle."""
+    spatial, window, dtype, scale, tokens = _random_geometry(index)
+    gen = torch.Generator().manual_seed(7100 + index)
+    q, k, v, dout = (torch.randn(1, 2, tokens, 64, generator=gen).to(dtype).cuda() for _ in range(4))
+    actual, names = _kernel_names(lambda: run(q, k, v, dout, spatial, window, scale))
+    assert "na_pipeline_forward" in names and "na_pipeline_backward_kv" in names
+    gate(actual, q, k, v, dout, spatial, window, scale)
+    from kohakufa_cute import native
+
+    assert native.device_status(reset=True) == 0
