@@ -42,6 +42,8 @@ WORKLOADS = {
                          published_tflops=70.0),
     "d128_4k": dict(B=1, Hq=16, Hkv=16, S=4096, D=128, dtype="bf16", causal=True, center_keys=False, seed=23,
                     graph=True, published_tflops=138.0),
+    "d64_4k": dict(B=1, Hq=16, Hkv=16, S=4096, D=64, dtype="bf16", causal=True, center_keys=False, seed=24,
+                   graph=True, published_tflops=118.0),
     "dit_masked": dict(B=2, Hq=24, Hkv=24, S=32768, D=128, dtype="bf16", causal=False, center_keys=False, seed=4,
                        masked_fraction=0.1),
     # The video/DiT shape as ONE long sequence sharded over the ranks (ring context parallelism).
