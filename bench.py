@@ -99,11 +99,12 @@ def make_host_inputs(w, rank, world=1):
         q *= 8.0
         k += 2.0 * torch.randn(B, Hkv, 1, D, generator=gen)  # N(0, 4): std 2 per component
         g *= math.sqrt(1e-3)  # N(0, 1e-3): std sqrt(1e-3)
-    tensors = [t.to(dtype).pin_memory() for t in (q, k, v, g)]
+    pin = (lambda t: t.pin_memory()) if torch.cuda.is_available() else (lambda t: t)
+    tensors = [pin(t.to(dtype)) for t in (q, k, v, g)]
     mask = None
     if "masked_fraction" in w:
         keep = total - int(total * w["masked_fraction"] + 0.5)
-        mask = (torch.arange(first, first + S) < keep)[None, None, None, :].expand(B, 1, 1, S).contiguous().pin_memory()
+        mask = pin((torch.arange(first, first + S) < keep)[None, None, None, :].expand(B, 1, 1, S).contiguous())
     return tensors, mask
 
 
