@@ -1,8 +1,11 @@
 """Builds libkfa.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
 
-    python kohakufa-cute_b200/build.py [--force]
+    python kohakufa-cute_b200/build.py [--force] [--phases]
 
 The shared library is written next to the Python package as ``kohakufa_cute/libkfa.so``.
+``--phases`` builds a second library, ``kohakufa_cute/libkfa_phases.so``, whose pipeline kernels record
+how many cycles each role of one CTA spends in each phase of its loop (see ``csrc/phase_clock.cuh``;
+``phase_profile.py`` runs it and prints the table).  The ordinary library carries none of that code.
 """
 
 import hashlib
@@ -22,24 +25,16 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-Wno-deprecated-gpu-targets"]
 
 
-if os.environ.get("KFA_TRACE"):  # tuning aid: cycle stamps from the CTA with this index
-    NVCC_FLAGS = NVCC_FLAGS + ["-DKFA_TRACE=" + os.environ["KFA_TRACE"]]
-
-
-if os.environ.get("KFA_DEFINES"):  # tuning aid: extra -D switches, space separated
-    NVCC_FLAGS = NVCC_FLAGS + ["-D" + d for d in os.environ["KFA_DEFINES"].split()]
-
-
 def _nvcc():
     return os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc" if os.path.exists("/usr/local/cuda/bin/nvcc") else "nvcc")
 
 
-def _digest(paths):
+def _digest(paths, flags):
     h = hashlib.sha256()
     for path in sorted(paths):
         with open(path, "rb") as f:
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(flags).encode())
     return h.hexdigest()
 
 
@@ -47,16 +42,19 @@ def sources():
     return [s for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
 
 
-def build(force=False, verbose=True):
-    os.makedirs(OBJ_DIR, exist_ok=True)
+def build(force=False, verbose=True, phases=False):
+    flags = NVCC_FLAGS + (["-DKFA_PHASES=1"] if phases else [])
+    obj_dir = OBJ_DIR + ("_phases" if phases else "")
+    lib = LIB.replace("libkfa.so", "libkfa_phases.so") if phases else LIB
+    os.makedirs(obj_dir, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".inl"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "kfa.h"))
     objects, jobs = [], []
     for src in sources():
         path = os.path.join(CSRC, src)
-        obj = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
+        obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
         stamp = obj + ".sha"
-        digest = _digest([path] + headers)
+        digest = _digest([path] + headers, flags)
         objects.append(obj)
         fresh = os.path.exists(obj) and os.path.exists(stamp) and open(stamp).read() == digest
         if force or not fresh:
@@ -64,7 +62,7 @@ def build(force=False, verbose=True):
 
     def compile_one(job):
         path, obj, stamp, digest = job
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", path, "-o", obj]
+        cmd = [_nvcc(), *flags, "-c", path, "-o", obj]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.check_call(cmd)
@@ -73,14 +71,14 @@ def build(force=False, verbose=True):
 
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:
         list(pool.map(compile_one, jobs))
-    if jobs or force or not os.path.exists(LIB):
-        cmd = [_nvcc(), "-shared", "-o", LIB, *objects, "-lcudart_static", "-ldl", "-lpthread", "-lrt",
+    if jobs or force or not os.path.exists(lib):
+        cmd = [_nvcc(), "-shared", "-o", lib, *objects, "-lcudart_static", "-ldl", "-lpthread", "-lrt",
                "-Wno-deprecated-gpu-targets"]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.check_call(cmd)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv))
+    print(build(force="--force" in sys.argv, phases="--phases" in sys.argv))

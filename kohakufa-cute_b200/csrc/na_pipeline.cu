@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
     if (sh.abort_word != 0) {
         // an earlier CTA gave up: skip straight to the tear-down
     } else if (warp == 5) {
-        if (lane == 0) {
+        if (elect_one()) {
             tma_prefetch_desc(&maps.q);
             tma_prefetch_desc(&maps.k);
             tma_prefetch_desc(&maps.v);
@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
                 }
         }
     } else if (warp == 4) {
-        if (lane == 0) {
+        if (elect_one()) {
             const uint32_t idesc_s =
                 umma_idesc(kTile, kTile, BF16 ? 1 : 0, false, false) | (p.scale < 0.f ? kUmmaNegateA : 0u);
             constexpr uint32_t idesc_o = umma_idesc(kTile, 64, BF16 ? 1 : 0, false, true);
@@ -130,10 +130,8 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
             int pos = 0, iter = 0;
             for (int j = next_tile(sh.bitmap, 0); j >= 0 && ok; j = next_tile(sh.bitmap, j + 1)) {
                 const int ks = pos % kRing;
-                KFA_TRACE_POINT(0, 1);
                 ok = mbar_wait(&sh.full[ks], (pos / kRing) & 1, abort_word, 21);
                 if (!ok) break;
-                KFA_TRACE_POINT(0, 2);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
@@ -144,10 +142,8 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
                 ++pos;
                 const int vs = pos % kRing;
                 ok = mbar_wait(&sh.full[vs], (pos / kRing) & 1, abort_word, 22);
-                KFA_TRACE_POINT(0, 3);
                 if (ok) ok = mbar_wait(&sh.p_ready, iter & 1, abort_word, 23);
                 if (!ok) break;
-                KFA_TRACE_POINT(0, 4);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk)
@@ -175,12 +171,9 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
         bool ok = true;
         for (int j = next_tile(sh.bitmap, 0); j >= 0 && ok; j = next_tile(sh.bitmap, j + 1)) {
             uint32_t vis[4] = {0, 0, 0, 0};
-            KFA_TRACE_POINT(1, 1);
             if (row_ok) box_mask<4>(p, box, j * kTile, p.Sk, vis);
-            KFA_TRACE_POINT(1, 2);
             ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 30);
             if (!ok) break;
-            KFA_TRACE_POINT(1, 3);
             tc_fence_after();
             // pass 1: hide what the row does not see (written back as -inf), maximum of the rest
             // 32-column chunks that no row of this warp can see are skipped (their weights are zero)
@@ -205,7 +198,6 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
             }
             const float mx = fmaxf(mx0, mx1);
             tmem_wait_st();
-            KFA_TRACE_POINT(1, 4);
             m_true = fmaxf(m_true, mx);
             const bool rebase = mx > m_used && (m_used == -INFINITY || (mx - m_used) * c2 > kRebase);
             float alpha = 1.f;
@@ -268,7 +260,6 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&sh.p_ready);
-            KFA_TRACE_POINT(1, 5);
             ++iter;
         }
         if (iter > 0 && ok) ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 31);
@@ -395,7 +386,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
     if (sh.abort_word != 0) {
         // an earlier CTA gave up: skip straight to the tear-down
     } else if (warp == 5) {
-        if (lane == 0) {
+        if (elect_one()) {
             tma_prefetch_desc(&maps.own0);
             tma_prefetch_desc(&maps.own1);
             tma_prefetch_desc(&maps.st0);
@@ -415,7 +406,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
             }
         }
     } else if (warp == 4) {
-        if (lane == 0) {
+        if (elect_one()) {
             const uint32_t idesc_s = umma_idesc(kTile, kSub, BF16 ? 1 : 0, false, false);
             const uint32_t idesc_neg = idesc_s | (p.scale < 0.f ? kUmmaNegateA : 0u);
             constexpr uint32_t idesc_g = umma_idesc(kTile, 64, BF16 ? 1 : 0, false, true);
@@ -718,15 +709,5 @@ cudaError_t launch_na_pipeline_backward(const AttnParams& p, bool bf16, int whic
     return bf16 ? backward_t<true, true>(p, st) : backward_t<true, false>(p, st);
 }
 
-#ifdef KFA_TRACE
-extern "C" __attribute__((visibility("default"))) int kfa_debug_trace_na(long long* out, int* counts) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_kfa_trace, sizeof(long long) * 4 * 1024);
-    cudaMemcpyFromSymbol(counts, g_kfa_trace_n, sizeof(int) * 4);
-    int zero[4] = {0, 0, 0, 0};
-    cudaMemcpyToSymbol(g_kfa_trace_n, zero, sizeof(zero));
-    return 0;
-}
-#endif
 
 }  // namespace kfa

@@ -1,10 +1,11 @@
-// Attention backward on the tensor-memory pipeline: kernel, support predicate and launchers.
-// The roles are described in pipeline_backward_roles.cuh / pipeline_backward_consumer.cuh.
+// Attention backward on the tensor-memory pipeline: the two gradient kernels, support predicate and launchers.
+// The roles are described in pipeline_backward_{kv,q}_roles.cuh / pipeline_backward_{kv,q}_consumer.cuh.
 #include <type_traits>
 
 #include "kfa_common.cuh"
 #include "launchers.h"
-#include "pipeline_backward_consumer.cuh"
+#include "pipeline_backward_kv_consumer.cuh"
+#include "pipeline_backward_q_consumer.cuh"
 #include "tensor_map.h"
 
 #include <atomic>
@@ -16,23 +17,24 @@ void pipeline_forward_forget();
 
 namespace {
 
+
 using namespace bwd;
 
-// MASKED = false is the instantiation for calls without a mask: the flag is cleared at compile time, so
-// none of the mask-table or mask-element code survives in it.
-template <int D, bool BF16, bool KV, bool MASKED>
-__global__ void __launch_bounds__(kThreads, 1) pipeline_backward(const __grid_constant__ Maps maps, AttnParams p) {
+// Key/value-gradient kernel.  MASKED = false is the instantiation for calls without a mask: the flag is
+// cleared at compile time, so none of the mask-table or mask-element code survives in it.
+template <int D, bool BF16, bool MASKED>
+__global__ void __launch_bounds__(kThreads, 1) pipeline_backward_kv(const __grid_constant__ Maps maps, AttnParams p) {
     if (!MASKED) p.has_mask = 0;
-    using C = Cfg<D>;
+    using C = kv::Cfg<D>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* s_owner = smem;                           // owner operands 1 and 2
-    uint8_t* s_ring = smem + 2 * C::kTileBytes;        // ring of streamed operand pairs
-    float* s_stats = reinterpret_cast<float*>(s_ring + C::kPairs * 2 * C::kTileBytes);
-    Shared& sh = *reinterpret_cast<Shared*>(reinterpret_cast<uint8_t*>(s_stats) + C::kStatsBytes);
+    uint8_t* s_owner = smem;                           // K and V of the owner tile
+    uint8_t* s_ring = smem + 2 * C::kTileBytes;        // ring of streamed (Q, dO) pairs
+    uint8_t* s_stat = s_ring + C::kPairs * 2 * C::kTileBytes;   // operand tiles of the statistics step
+    kv::Shared& sh = *reinterpret_cast<kv::Shared*>(s_stat + C::kStatsBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    Work<KV> w;
+    Work<true> w;
     w.init(p);
 
     if (threadIdx.x == 0) {
@@ -40,15 +42,17 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward(const __grid_co
         mbar_init(&sh.owner_full, 1);
         for (int s = 0; s < C::kPairs; ++s) {
             mbar_init(&sh.pair_full[s], 1);
-            mbar_init(&sh.pair_empty[s], 2);  // both MMA issuers release a slot
+            mbar_init(&sh.pair_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&sh.sdp_ready[s], 2);   // S from issuer 0, dP from issuer 1
-            mbar_init(&sh.done[s], kConsumers);
             mbar_init(&sh.stats_full[s], 1);
-            mbar_init(&sh.stats_empty[s], kConsumers);
+            mbar_init(&sh.stats_empty[s], 1);
         }
-        mbar_init(&sh.final_done, 2);
+        mbar_init(&sh.s_ready, 1);
+        mbar_init(&sh.dp_ready, 1);
+        mbar_init(&sh.p_done, kConsumers);
+        mbar_init(&sh.ds_done, kConsumers);
+        mbar_init(&sh.final_done, 1);
         mbar_fence_init();
     }
     if (warp == kRoleWarp) {
@@ -61,27 +65,93 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward(const __grid_co
     const uint32_t tmem = sh.tmem_base;
     const bool dead = sh.abort_word != 0;  // set before the barrier above: skip straight to the tear-down
 
-    // With two consumer warpgroups (384 threads, 168 registers at launch) registers move from the role
-    // warpgroup to the consumers; with four (640 threads, 96 registers) every role fits as launched.
+    // Registers move from the role warpgroup to the two consumer warpgroups.
     if (dead) {
     } else if (warp >= kRoleWarp) {
-        if (kGroups == 2) reg_dealloc<96>();
-        if (warp <= kRoleWarp + 1) {
-            if (lane == 0) mma_role<D, BF16, KV>(p, w, sh, tmem, s_owner, s_ring, warp - kRoleWarp);
+        reg_dealloc<96>();
+        if (warp == kRoleWarp) {
+            if (elect_one()) kv::mma_role<D, BF16>(p, w, sh, tmem, s_owner, s_ring, s_stat);
+        } else if (warp == kRoleWarp + 1) {
         } else if (warp == kRoleWarp + 2) {
-            if (lane == 0) loader_role<D, KV>(maps, p, w, sh, s_owner, s_ring);
+            if (elect_one()) kv::loader_role<D>(maps, p, w, sh, s_owner, s_ring);
         } else {
-            if (KV) stats_role<KV>(p, w, sh, s_stats, lane);
+            kv::stats_role(p, w, sh, s_stat, lane);
         }
     } else {
-        if (kGroups == 2) reg_alloc<200>();
-        consumer_role<D, BF16, KV>(p, w, sh, tmem, s_stats, warp >> 2, warp, lane);
+        reg_alloc<200>();
+        kv::consumer_role<D, BF16>(p, w, sh, tmem, warp >> 2, warp, lane);
     }
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && sh.abort_word != 0 && sh.abort_word != 90) {  // 90 = skipped: already reported
         *p.status = 2000 + sh.abort_word;
         *reinterpret_cast<volatile int*>(p.abort_flag) = 1;  // the remaining CTAs of this and later launches skip their work
+    }
+    if (warp == kRoleWarp) tmem_dealloc(tmem, 512);
+}
+
+// Query-gradient kernel.
+template <int D, bool BF16, bool MASKED>
+__global__ void __launch_bounds__(kThreads, 1) pipeline_backward_q(const __grid_constant__ Maps maps, AttnParams p) {
+    if (!MASKED) p.has_mask = 0;
+    using C = q::Cfg<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* s_owner = smem;                                       // Q and dO of the owner tile
+    uint8_t* s_keys = smem + 2 * C::kTileBytes;                    // ring of K tiles
+    uint8_t* s_values = s_keys + C::kKeySlots * C::kTileBytes;     // ring of V tiles
+    q::Shared& sh = *reinterpret_cast<q::Shared*>(s_values + C::kValueSlots * C::kTileBytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    Work<false> w;
+    w.init(p);
+
+    if (threadIdx.x == 0) {
+        sh.abort_word = *reinterpret_cast<volatile int*>(p.abort_flag) != 0 ? 90 : 0;  // 90: an earlier CTA gave up
+        mbar_init(&sh.owner_full, 1);
+        for (int s = 0; s < q::kMaxSlots; ++s) {
+            mbar_init(&sh.k_full[s], 1);
+            mbar_init(&sh.k_empty[s], 2);  // the S product and the dQ product both read a K tile
+            mbar_init(&sh.v_full[s], 1);
+            mbar_init(&sh.v_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&sh.s_ready[s], 1);
+            mbar_init(&sh.s_free[s], 1);
+        }
+        mbar_init(&sh.dp_ready, 1);
+        mbar_init(&sh.dp_free, kConsumers);
+        mbar_init(&sh.ds_done, kConsumers);
+        mbar_init(&sh.final_done, 2);
+        mbar_fence_init();
+    }
+    if (warp == kRoleWarp) {
+        tmem_alloc(&sh.tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    const bool dead = sh.abort_word != 0;
+
+    if (dead) {
+    } else if (warp >= kRoleWarp) {
+        reg_dealloc<96>();
+        if (warp <= kRoleWarp + 1) {
+            if (elect_one()) q::mma_role<D, BF16>(p, w, sh, tmem, s_owner, s_keys, s_values, warp - kRoleWarp);
+        } else if (warp == kRoleWarp + 2) {
+            if (elect_one()) q::loader_role<D>(maps, p, w, sh, s_owner, s_keys, s_values);
+        }
+    } else {
+        reg_alloc<200>();
+        q::consumer_role<D, BF16>(p, w, sh, tmem, warp >> 2, warp, lane);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && sh.abort_word != 0 && sh.abort_word != 90) {
+        *p.status = 2000 + sh.abort_word;
+        *reinterpret_cast<volatile int*>(p.abort_flag) = 1;
     }
     if (warp == kRoleWarp) tmem_dealloc(tmem, 512);
 }
@@ -117,9 +187,12 @@ std::atomic<int> g_configured{0};
 
 template <int D, bool BF16, bool KV>
 cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
-    using C = Cfg<D>;
-    auto kernel = p.has_mask ? pipeline_backward<D, BF16, KV, true> : pipeline_backward<D, BF16, KV, false>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    constexpr int kSmem = KV ? kv::Cfg<D>::kSmemBytes : q::Cfg<D>::kSmemBytes;
+    using Kernel = void (*)(const Maps, AttnParams);
+    Kernel kernel;
+    if (KV) kernel = p.has_mask ? pipeline_backward_kv<D, BF16, true> : pipeline_backward_kv<D, BF16, false>;
+    else kernel = p.has_mask ? pipeline_backward_q<D, BF16, true> : pipeline_backward_q<D, BF16, false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e != cudaSuccess) return e;
     constexpr int variant = (D == 128 ? 0 : 4) + (BF16 ? 0 : 2) + (KV ? 1 : 0);
     if (!(g_configured.load() & (1 << variant))) g_configured |= 1 << variant;
@@ -131,7 +204,7 @@ cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
     if (!encode_bhsd_map(&maps.g, p.dout, dt, p.D, p.Sq, p.Hq, p.B, p.gs, 64, kTile)) return cudaErrorInvalidValue;
     const int64_t tiles = KV ? (p.Sk + kTile - 1) / kTile : (p.Sq + kTile - 1) / kTile;
     const int64_t grid = tiles * p.B * (KV ? p.Hkv : p.Hq);
-    kernel<<<(unsigned)grid, kThreads, C::kSmemBytes, st>>>(maps, p);
+    kernel<<<(unsigned)grid, kThreads, kSmem, st>>>(maps, p);
     return cudaGetLastError();
 }
 
@@ -175,16 +248,7 @@ cudaError_t launch_pipeline_delta(const AttnParams& p, bool bf16, cudaStream_t s
     return cudaGetLastError();
 }
 
-#ifdef KFA_TRACE
-extern "C" __attribute__((visibility("default"))) int kfa_debug_trace(long long* out, int* counts) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_kfa_trace, sizeof(long long) * 4 * 1024);
-    cudaMemcpyFromSymbol(counts, g_kfa_trace_n, sizeof(int) * 4);
-    int zero[4] = {0, 0, 0, 0};
-    cudaMemcpyToSymbol(g_kfa_trace_n, zero, sizeof(zero));
-    return 0;
-}
-#endif
+KFA_PHASE_EXPORT(kfa_debug_phases_bwd)
 
 int pipeline_configured_variants() { return pipeline_forward_variants() + __builtin_popcount(g_configured.load()); }
 void pipeline_forget_variants() {

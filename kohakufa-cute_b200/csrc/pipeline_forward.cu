@@ -32,6 +32,7 @@
 namespace kfa {
 namespace {
 
+
 constexpr int kTileQ = 128;
 constexpr int kTileK = 128;
 constexpr int kThreads = 384;  // three warpgroups: softmax 0, softmax 1, (MMA, loader, 2 idle warps)
@@ -159,7 +160,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
       reg_dealloc<88>();
       if (warp == 9) {
         // ------------------------------------------------------------ loader
-        if (lane == 0) {
+        if (elect_one()) {
             tma_prefetch_desc(&maps.q);
             tma_prefetch_desc(&maps.k);
             tma_prefetch_desc(&maps.v);
@@ -189,7 +190,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
         }
       } else if (warp == 8) {
         // ------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        if (elect_one()) {
             // a negative scale takes the maximum over -S: negate the A operand of the score product
             const uint32_t idesc_s =
                 umma_idesc(kTileQ, kTileK, BF16 ? 1 : 0, false, false) | (p.scale < 0.f ? kUmmaNegateA : 0u);
@@ -216,6 +217,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
             };
             bool ok = mbar_wait(&sh.q_full, 0, abort_word, 20);
             int slot_use = 0, iter[2] = {0, 0};
+            PH_DECL;
             // first visible key tile
             int j = 0;
             while (j < n_max && state_of(j) == 0) ++j;
@@ -244,17 +246,18 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                     k_par = (slot_use / Cfg::kStages) & 1;
                     ++slot_use;
                 }
+                PH(5);
                 ok = mbar_wait(&sh.kv_full[v_slot], v_par, abort_word, 22);
+                PH(0);
                 bool k_waited = false;
                 for (int t = 0; t < 2 && ok; ++t) {
                     if (j >= n_t[t]) continue;
-                    KFA_TRACE_POINT(0, 1);
                     ok = mbar_wait(&sh.p_ready[t], iter[t] & 1, abort_word, 23 + t);
                     if (!ok) break;
-                    KFA_TRACE_POINT(0, 2);
+                    PH(1);
                     tc_fence_after();
                     issue_o(t, v_slot, iter[t] > 0);
-                    KFA_TRACE_POINT(0, 3);
+                    PH(2);
                     if (jn < n_t[t]) {
                         if (!k_waited) {
                             ok = mbar_wait(&sh.kv_full[k_slot], k_par, abort_word, 25);
@@ -262,10 +265,11 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                             tc_fence_after();
                             k_waited = true;
                         }
+                        PH(3);
                         issue_s(t, k_slot);
                     }
                     umma_commit(&sh.s_ready[t]);
-                    KFA_TRACE_POINT(0, 4);
+                    PH(4);
                     ++iter[t];
                 }
                 if (!ok) break;
@@ -273,6 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                 if (k_slot >= 0) umma_commit(&sh.kv_empty[k_slot]);
                 j = jn;
             }
+            PH_FLUSH(2);
         }
       }
     } else {
@@ -292,13 +297,14 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
         float m_used = -INFINITY, m_true = -INFINITY, l = 0.f;
         int iter = 0;
         bool ok = true;
+        PH_DECL;
         for (int j = 0; j < n_t[t] && ok; ++j) {
             const int state = state_of(j);
             if (state == 0) continue;
-            KFA_TRACE_POINT(1 + t, 1);
+            PH(5);
             ok = mbar_wait(&sh.s_ready[t], iter & 1, abort_word, 30 + t);
             if (!ok) break;
-            KFA_TRACE_POINT(1 + t, 2);
+            PH(0);
             tc_fence_after();
             // scores arrive already multiplied by sign(scale) (negated A operand for negative scales)
             float s[kTileK];
@@ -310,7 +316,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                 for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(r[i]);
             }
             tmem_wait_ld();
-            KFA_TRACE_POINT(1 + t, 3);
+            PH(1);
             const int key0 = j * kTileK;
             // leading columns of this tile that pass the sequence-end and causal bounds for this row
             int lim = p.Sk - key0;
@@ -352,7 +358,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                     tmem_st32(o_addr + c, r);
                 }
             }
-            KFA_TRACE_POINT(1 + t, 4);
+            PH(2);
             const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
             const uint64_t m_pair = f2_pack(m_safe, m_safe);
             uint64_t sum_a = f2_pack(0.f, 0.f), sum_b = sum_a;
@@ -382,12 +388,14 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                 f2_unpack(sum_b, x2, x3);
                 l += (x0 + x1) + (x2 + x3);
             }
+            PH(3);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&sh.p_ready[t]);
-            KFA_TRACE_POINT(1 + t, 5);
+            PH(4);
             ++iter;
         }
+        if ((threadIdx.x & 127) == 0) PH_FLUSH(t);
         // epilogue: wait for the last product, normalise, store
         if (ok && iter == 0 && row < p.Sq && n_t[t] > 0) {
             // every key tile of this row is hidden: zero output, empty statistics
@@ -482,16 +490,7 @@ cudaError_t launch_pipeline_forward(const AttnParams& p, bool bf16, cudaStream_t
     return bf16 ? launch_t<64, true>(p, st) : launch_t<64, false>(p, st);
 }
 
-#ifdef KFA_TRACE
-extern "C" __attribute__((visibility("default"))) int kfa_debug_trace_fwd(long long* out, int* counts) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_kfa_trace, sizeof(long long) * 4 * 1024);
-    cudaMemcpyFromSymbol(counts, g_kfa_trace_n, sizeof(int) * 4);
-    int zero[4] = {0, 0, 0, 0};
-    cudaMemcpyToSymbol(g_kfa_trace_n, zero, sizeof(zero));
-    return 0;
-}
-#endif
+KFA_PHASE_EXPORT(kfa_debug_phases_fwd)
 
 int pipeline_forward_variants() { return __builtin_popcount(g_configured.load()); }
 void pipeline_forward_forget() { g_configured = 0; }

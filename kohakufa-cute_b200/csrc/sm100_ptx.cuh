@@ -13,30 +13,28 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
-// Optional cycle-stamp tracing of one CTA for tuning (compiled in only with -DKFA_TRACE).
-#ifdef KFA_TRACE
-static __device__ long long g_kfa_trace[4][1024];
-static __device__ int g_kfa_trace_n[4];
-#define KFA_TRACE_POINT(stream, tag)                                              \
-    do {                                                                          \
-        if (blockIdx.x == KFA_TRACE && (threadIdx.x == 0 || threadIdx.x == 128 || threadIdx.x == 256)) {                 \
-            int n_ = g_kfa_trace_n[stream];                                       \
-            if (n_ < 1024) {                                                      \
-                g_kfa_trace[stream][n_] = (clock64() << 4) | (tag);               \
-                g_kfa_trace_n[stream] = n_ + 1;                                   \
-            }                                                                     \
-        }                                                                         \
-    } while (0)
-#else
-#define KFA_TRACE_POINT(stream, tag) \
-    do {                             \
-    } while (0)
-#endif
+#include "phase_clock.cuh"
 
 namespace kfa {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// True in exactly one lane of a fully converged warp.  A role that only this lane runs keeps its
+// warp-uniform values (descriptors, addresses, loop state) in uniform registers, which makes issuing
+// tcgen05.mma markedly cheaper than from a lane picked by a thread-index test: the issuing thread then
+// runs ahead of the tensor core instead of pacing it.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " elect.sync _|p, 0xffffffff;\n"
+        " selp.u32 %0, 1, 0, p;\n"
+        "}"
+        : "=r"(pred));
+    return pred != 0;
 }
 
 // ----------------------------------------------------------------- mbarrier

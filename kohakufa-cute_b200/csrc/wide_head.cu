@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
         // --------------------------------------------------------------- loaders
         // Two loading threads take alternate ring positions: one thread's stream of 16 KB boxes does not
         // keep the ring full.
-        if (lane == 0) {
+        if (elect_one()) {
             const int me = warp == 5 ? 0 : 1;
             tma_prefetch_desc(&maps.a);
             tma_prefetch_desc(&maps.b);
@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
         }
     } else if (warp == 4 || warp == 6) {
         // ----------------------------------------------------------- MMA issuers
-        if (lane == 0) {
+        if (elect_one()) {
             const int who = warp == 4 ? 0 : 1;
             const uint32_t idesc_s =
                 umma_idesc(kTile, kTile, BF16 ? 1 : 0, false, false) | (p.scale < 0.f ? kUmmaNegateA : 0u);
@@ -178,13 +178,11 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
                 if (key_tile_state(p, b, h, j) == 0) continue;
                 // S_a also holds P_low of the previous tile, which issuer 1's product is still reading
                 if (who == 0 && iter > 0) ok = mbar_wait(&sh.pvb_done, (iter - 1) & 1, abort_word, 24);
-                KFA_TRACE_POINT(0, 1);
                 for (int c = 0; c < chunks && ok; ++c, ++pos) {
                     if ((c & 1) != who) continue;
                     const int slot = pos % kRing;
                     ok = mbar_wait(&sh.full[slot], (pos / kRing) & 1, abort_word, 21);
                     if (!ok) break;
-                    KFA_TRACE_POINT(0, 2);
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
@@ -198,10 +196,8 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
                 for (int i = 0; i < v_count && ok; ++i)
                     ok = mbar_wait(&sh.full[(pos + v_first + i) % kRing], ((pos + v_first + i) / kRing) & 1, abort_word,
                                    22);
-                KFA_TRACE_POINT(0, 3);
                 if (ok) ok = mbar_wait(&sh.p_ready, iter & 1, abort_word, 23);
                 if (!ok) break;
-                KFA_TRACE_POINT(0, 4);
                 tc_fence_after();
                 if (v_count > 0) {
 #pragma unroll
@@ -232,10 +228,8 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int state = key_tile_state(p, b, h, j);
             if (state == 0) continue;
-            KFA_TRACE_POINT(1, 1);
             ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 30);
             if (!ok) break;
-            KFA_TRACE_POINT(1, 2);
             tc_fence_after();
             float s[kTile];
 #pragma unroll
@@ -318,7 +312,6 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&sh.p_ready);
-            KFA_TRACE_POINT(1, 3);
             ++iter;
         }
         T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] + (int64_t)row * p.os[2] +
@@ -440,7 +433,7 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
     if (sh.abort_word != 0) {
         // an earlier CTA gave up: skip straight to the tear-down
     } else if (warp == 5) {
-        if (lane == 0) {
+        if (elect_one()) {
             tma_prefetch_desc(&maps.a);
             tma_prefetch_desc(&maps.b);
             mbar_expect_tx(&sh.own_full, chunks * kChunkBytes);
@@ -460,7 +453,7 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
     } else if (warp == 4 || warp == 6) {
         // Two issuers share the contraction: issuer 0 the even 64-channel chunks, issuer 1 the odd ones,
         // each into its own partial accumulator (columns +0 and +128 of the score buffer).
-        if (lane == 0) {
+        if (elect_one()) {
             const int who = warp == 4 ? 0 : 1;
             const uint32_t idesc = umma_idesc(kTile, kTile, BF16 ? 1 : 0, false, false) |
                                    (MODE == 0 && p.scale < 0.f ? kUmmaNegateA : 0u);
@@ -670,7 +663,7 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Grad
     if (sh.abort_word != 0) {
         // an earlier CTA gave up: skip straight to the tear-down
     } else if (warp == 5) {
-        if (lane == 0 && units > 0) {
+        if (units > 0 && elect_one()) {
             tma_prefetch_desc(map_a);
             tma_prefetch_desc(map_b);
             bool ok = true;
@@ -693,7 +686,7 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Grad
             }
         }
     } else if (warp == 4) {
-        if (lane == 0 && units > 0) {
+        if (units > 0 && elect_one()) {
             const uint32_t idesc = umma_idesc(kTile, 64 * hc, BF16 ? 1 : 0, KV, true);
             const uint32_t base = smem_u32(smem);
             const uint64_t a_desc = KV ? umma_desc_sw128(base, kChunkBytes, 1024) : umma_desc_sw128(base, 16, 1024);
@@ -904,15 +897,5 @@ cudaError_t launch_wide_backward(const AttnParams& p, bool bf16, int step, void*
     }
 }
 
-#ifdef KFA_TRACE
-extern "C" __attribute__((visibility("default"))) int kfa_debug_trace_wide(long long* out, int* counts) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_kfa_trace, sizeof(long long) * 4 * 1024);
-    cudaMemcpyFromSymbol(counts, g_kfa_trace_n, sizeof(int) * 4);
-    int zero[4] = {0, 0, 0, 0};
-    cudaMemcpyToSymbol(g_kfa_trace_n, zero, sizeof(zero));
-    return 0;
-}
-#endif
 
 }  // namespace kfa
