@@ -53,6 +53,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward_kv(const __grid
         mbar_init(&sh.p_done, kConsumers);
         mbar_init(&sh.ds_done, kConsumers);
         mbar_init(&sh.final_done, 1);
+        mbar_init(&sh.out_staged, kConsumers);
         mbar_fence_init();
     }
     if (warp == kRoleWarp) {
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward_kv(const __grid
         }
     } else {
         reg_alloc<200>();
-        kv::consumer_role<D, BF16>(p, w, sh, tmem, warp >> 2, warp, lane);
+        kv::consumer_role<D, BF16>(maps, p, w, sh, tmem, s_owner, warp >> 2, warp, lane);
     }
     tc_fence_before();
     __syncthreads();
@@ -123,6 +124,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward_q(const __grid_
         mbar_init(&sh.dp_free, kConsumers);
         mbar_init(&sh.ds_done, kConsumers);
         mbar_init(&sh.final_done, 2);
+        mbar_init(&sh.out_staged, kConsumers);
         mbar_fence_init();
     }
     if (warp == kRoleWarp) {
@@ -145,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward_q(const __grid_
         }
     } else {
         reg_alloc<200>();
-        q::consumer_role<D, BF16>(p, w, sh, tmem, warp >> 2, warp, lane);
+        q::consumer_role<D, BF16>(maps, p, w, sh, tmem, s_owner, warp >> 2, warp, lane);
     }
     tc_fence_before();
     __syncthreads();
@@ -202,6 +204,14 @@ cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
     if (!encode_bhsd_map(&maps.k, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kTile)) return cudaErrorInvalidValue;
     if (!encode_bhsd_map(&maps.v, p.v, dt, p.D, p.Sk, p.Hkv, p.B, p.vs, 64, kTile)) return cudaErrorInvalidValue;
     if (!encode_bhsd_map(&maps.g, p.dout, dt, p.D, p.Sq, p.Hq, p.B, p.gs, 64, kTile)) return cudaErrorInvalidValue;
+    if (KV) {
+        if (!encode_bhsd_map(&maps.dk, p.dk, dt, p.D, p.Sk, p.Hkv, p.B, p.dks, 64, kTile)) return cudaErrorInvalidValue;
+        if (!encode_bhsd_map(&maps.dv, p.dv, dt, p.D, p.Sk, p.Hkv, p.B, p.dvs, 64, kTile)) return cudaErrorInvalidValue;
+        maps.dq = maps.dk;
+    } else {
+        if (!encode_bhsd_map(&maps.dq, p.dq, dt, p.D, p.Sq, p.Hq, p.B, p.dqs, 64, kTile)) return cudaErrorInvalidValue;
+        maps.dk = maps.dv = maps.dq;
+    }
     const int64_t tiles = KV ? (p.Sk + kTile - 1) / kTile : (p.Sq + kTile - 1) / kTile;
     const int64_t grid = tiles * p.B * (KV ? p.Hkv : p.Hq);
     kernel<<<(unsigned)grid, kThreads, kSmem, st>>>(maps, p);

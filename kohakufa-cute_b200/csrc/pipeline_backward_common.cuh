@@ -14,6 +14,7 @@ constexpr int kThreads = kConsumers + 128;
 
 struct Maps {
     CUtensorMap q, k, v, g;  // g = dO
+    CUtensorMap dq, dk, dv;  // outputs, stored as whole tiles from shared memory
 };
 
 // Combined state of the 128 queries [q_lo, q_lo + 128) x 128 keys of tile j for query head h, from

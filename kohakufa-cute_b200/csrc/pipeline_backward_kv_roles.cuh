@@ -55,6 +55,7 @@ struct Shared {
     uint64_t stats_full[2];
     uint64_t stats_empty[2];
     uint64_t final_done;
+    uint64_t out_staged;   // every consumer has put its part of the gradient tiles into shared memory
     uint32_t tmem_base;
     int abort_word;
 };

@@ -17,8 +17,8 @@ namespace bwd {
 namespace q {
 
 template <int D, bool BF16>
-__device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<false>& w, Shared& sh, uint32_t tmem,
-                                              int wg, int warp, int lane) {
+__device__ __forceinline__ void consumer_role(const Maps& maps, const AttnParams& p, const Work<false>& w, Shared& sh,
+                                              uint32_t tmem, uint8_t* s_owner, int wg, int warp, int lane) {
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
     volatile int* abort_word = &sh.abort_word;
     const int r = (warp & 3) * 32 + lane;  // query row inside the tile == tensor-memory lane
@@ -150,6 +150,9 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<fa
     if (ok) ok = mbar_wait(&sh.final_done, 0, abort_word, 150);
     if (!ok) return;
     tc_fence_after();
+    // The scaled tile goes through the (now dead) Q buffer in the swizzled box layout and leaves as tiled
+    // stores: whole 128-byte lines instead of 16 bytes per row and instruction.  Rows beyond the sequence
+    // end are not written by the store.
     const uint32_t acc = lane_base + kColGrad + ch0;
     const float mul = p.scale;
     constexpr int kStep = kHalf < 32 ? 16 : 32;
@@ -158,17 +161,24 @@ __device__ __forceinline__ void consumer_role(const AttnParams& p, const Work<fa
         uint32_t v[kStep];
         tmem_ld(acc + c, v);
         tmem_wait_ld();
-        if (out) {
 #pragma unroll
-            for (int e = 0; e < kStep; e += 8) {
-                uint4 o;
-                o.x = pack2<BF16>(__uint_as_float(v[e]) * mul, __uint_as_float(v[e + 1]) * mul);
-                o.y = pack2<BF16>(__uint_as_float(v[e + 2]) * mul, __uint_as_float(v[e + 3]) * mul);
-                o.z = pack2<BF16>(__uint_as_float(v[e + 4]) * mul, __uint_as_float(v[e + 5]) * mul);
-                o.w = pack2<BF16>(__uint_as_float(v[e + 6]) * mul, __uint_as_float(v[e + 7]) * mul);
-                *reinterpret_cast<uint4*>(out + c + e) = o;
-            }
+        for (int e = 0; e < kStep; e += 8) {
+            uint4 o;
+            o.x = pack2<BF16>(__uint_as_float(v[e]) * mul, __uint_as_float(v[e + 1]) * mul);
+            o.y = pack2<BF16>(__uint_as_float(v[e + 2]) * mul, __uint_as_float(v[e + 3]) * mul);
+            o.z = pack2<BF16>(__uint_as_float(v[e + 4]) * mul, __uint_as_float(v[e + 5]) * mul);
+            o.w = pack2<BF16>(__uint_as_float(v[e + 6]) * mul, __uint_as_float(v[e + 7]) * mul);
+            const int chunk = (ch0 + c + e) >> 3;
+            *reinterpret_cast<uint4*>(s_owner + (chunk >> 3) * (kTile * 128) + sw128_chunk(r, chunk & 7)) = o;
         }
+    }
+    fence_async_smem();
+    mbar_arrive(&sh.out_staged);
+    if (threadIdx.x == 0 && mbar_wait(&sh.out_staged, 0, abort_word, 151)) {
+        for (int c = 0; c < Cfg<D>::kChunks; ++c)
+            tma_store_4d(&maps.dq, s_owner + c * (kTile * 128), c * 64, w.owner0, w.head, w.b);
+        tma_store_commit();
+        tma_store_wait_read();
     }
 }
 

@@ -41,6 +41,7 @@ struct Shared {
     uint64_t dp_free;      // every consumer holds its dP values
     uint64_t ds_done;      // every consumer stored its dS_low
     uint64_t final_done;
+    uint64_t out_staged;   // every consumer has put its part of the gradient tile into shared memory
     uint32_t tmem_base;
     int abort_word;
 };

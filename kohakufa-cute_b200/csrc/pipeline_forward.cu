@@ -49,7 +49,7 @@ struct FwdCfg {
 };
 
 struct FwdMaps {
-    CUtensorMap q, k, v;
+    CUtensorMap q, k, v, o;
 };
 
 struct Shared {
@@ -58,6 +58,7 @@ struct Shared {
     uint64_t kv_empty[6];
     uint64_t s_ready[2];
     uint64_t p_ready[2];
+    uint64_t o_staged[2];  // every softmax thread of the tile has put its output row into shared memory
     uint32_t tmem_base;
     int abort_word;
     uint8_t tile_state[kMaxKeyTiles];  // per key tile of this CTA: 0 hidden, 1 mixed, 2 visible (masked calls)
@@ -136,6 +137,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
         for (int t = 0; t < 2; ++t) {
             mbar_init(&sh.s_ready[t], 1);
             mbar_init(&sh.p_ready[t], kTileQ);
+            mbar_init(&sh.o_staged[t], kTileQ);
         }
         mbar_fence_init();
     }
@@ -410,26 +412,34 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
             if (ok) ok = mbar_wait(&sh.s_ready[t], iter & 1, abort_word, 32 + t);
             if (ok) {
                 tc_fence_after();
-                using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-                T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] +
-                          (int64_t)row * p.os[2];
                 const float den = l > 0.f ? l : 1.f;
+                const float inv_den = 1.f / den;  // one division per row; the elements are multiplied
+                // The normalised tile goes through this tile's (now dead) Q buffer in the swizzled box layout and
+                // leaves as tiled stores: whole 128-byte lines instead of 16 bytes per row and instruction.
+                uint8_t* stage = sQ + t * Cfg::kTileBytes;
 #pragma unroll
                 for (int c = 0; c < D; c += 32) {
                     uint32_t r[32];
                     tmem_ld32(o_addr + c, r);
                     tmem_wait_ld();
-                    if (row < p.Sq) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            uint4 w;
-                            w.x = pack2<BF16>(__uint_as_float(r[i]) / den, __uint_as_float(r[i + 1]) / den);
-                            w.y = pack2<BF16>(__uint_as_float(r[i + 2]) / den, __uint_as_float(r[i + 3]) / den);
-                            w.z = pack2<BF16>(__uint_as_float(r[i + 4]) / den, __uint_as_float(r[i + 5]) / den);
-                            w.w = pack2<BF16>(__uint_as_float(r[i + 6]) / den, __uint_as_float(r[i + 7]) / den);
-                            *reinterpret_cast<uint4*>(orow + c + i) = w;
-                        }
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        w.x = pack2<BF16>(__uint_as_float(r[i]) * inv_den, __uint_as_float(r[i + 1]) * inv_den);
+                        w.y = pack2<BF16>(__uint_as_float(r[i + 2]) * inv_den, __uint_as_float(r[i + 3]) * inv_den);
+                        w.z = pack2<BF16>(__uint_as_float(r[i + 4]) * inv_den, __uint_as_float(r[i + 5]) * inv_den);
+                        w.w = pack2<BF16>(__uint_as_float(r[i + 6]) * inv_den, __uint_as_float(r[i + 7]) * inv_den);
+                        const int chunk = (c + i) >> 3;  // 16-byte chunk of the row: box chunk / 8, position chunk % 8
+                        *reinterpret_cast<uint4*>(stage + (chunk >> 3) * (kTileQ * 128) + sw128_chunk(row_in_tile, chunk & 7)) = w;
                     }
+                }
+                fence_async_smem();
+                mbar_arrive(&sh.o_staged[t]);
+                if (row_in_tile == 0 && mbar_wait(&sh.o_staged[t], 0, abort_word, 34 + t)) {
+                    for (int c = 0; c < Cfg::kChunks; ++c)
+                        tma_store_4d(&maps.o, stage + c * (kTileQ * 128), c * 64, q0 + t * kTileQ, h, b);
+                    tma_store_commit();
+                    tma_store_wait_read();
                 }
                 if (row < p.Sq) {
                     const int64_t si = ((int64_t)b * p.Hq + h) * p.Sq + row;
@@ -465,6 +475,7 @@ cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
     if (!encode_bhsd_map(&maps.q, p.q, dt, p.D, p.Sq, p.Hq, p.B, p.qs, 64, kTileQ)) return cudaErrorInvalidValue;
     if (!encode_bhsd_map(&maps.k, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kTileK)) return cudaErrorInvalidValue;
     if (!encode_bhsd_map(&maps.v, p.v, dt, p.D, p.Sk, p.Hkv, p.B, p.vs, 64, kTileK)) return cudaErrorInvalidValue;
+    if (!encode_bhsd_map(&maps.o, p.out, dt, p.D, p.Sq, p.Hq, p.B, p.os, 64, kTileQ)) return cudaErrorInvalidValue;
     const int64_t grid = (int64_t)((p.Sq + 2 * kTileQ - 1) / (2 * kTileQ)) * p.B * p.Hq;
     kernel<<<(unsigned)grid, kThreads, Cfg::kSmemBytes, st>>>(maps, p);
     return cudaGetLastError();

@@ -103,6 +103,21 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+// Tiled 4-D store from this CTA's shared memory (the box of the tensor map); elements beyond the tensor's
+// extents are not written.  Stores join the thread's bulk group: commit, then wait until the engine has
+// read the shared-memory source before that memory is reused or the CTA exits.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map),
+                 "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Byte offset of the 16-byte chunk j (0..7) of row r inside a box of 64 16-bit channels laid out with the
+// 128-byte swizzle (what the tiled loads produce and the tiled stores expect).
+__device__ __forceinline__ uint32_t sw128_chunk(int r, int j) {
+    return static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4));
+}
 // Makes generic-proxy writes to shared memory visible to the async proxy
 // (tensor-core operand reads, TMA stores).
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

@@ -330,6 +330,7 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
             if (ok) {
                 tc_fence_after();
                 const float den = l > 0.f ? l : 1.f;
+                const float inv_den = 1.f / den;  // one division per row; the elements are multiplied
                 for (int c = 0; c < width; c += 32) {
                     uint32_t r[32];
                     tmem_ld32(o_addr + c, r);
@@ -338,10 +339,10 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
                             uint4 w;
-                            w.x = pack2<BF16>(__uint_as_float(r[i]) / den, __uint_as_float(r[i + 1]) / den);
-                            w.y = pack2<BF16>(__uint_as_float(r[i + 2]) / den, __uint_as_float(r[i + 3]) / den);
-                            w.z = pack2<BF16>(__uint_as_float(r[i + 4]) / den, __uint_as_float(r[i + 5]) / den);
-                            w.w = pack2<BF16>(__uint_as_float(r[i + 6]) / den, __uint_as_float(r[i + 7]) / den);
+                            w.x = pack2<BF16>(__uint_as_float(r[i]) * inv_den, __uint_as_float(r[i + 1]) * inv_den);
+                            w.y = pack2<BF16>(__uint_as_float(r[i + 2]) * inv_den, __uint_as_float(r[i + 3]) * inv_den);
+                            w.z = pack2<BF16>(__uint_as_float(r[i + 4]) * inv_den, __uint_as_float(r[i + 5]) * inv_den);
+                            w.w = pack2<BF16>(__uint_as_float(r[i + 6]) * inv_den, __uint_as_float(r[i + 7]) * inv_den);
                             *reinterpret_cast<uint4*>(orow + c + i) = w;
                         }
                     }
