@@ -61,6 +61,16 @@ KFA_API int kfa_version(void);
 KFA_API const char* kfa_last_error(void);
 
 /*
+ * Sets up the per-device state of the device that is current on the calling thread (a status word in
+ * mapped host memory and a small flag in device memory).  The first launching call on a device does
+ * the same implicitly; call kfa_init() instead when that first call would otherwise fall inside a
+ * stream capture, where allocating is not allowed (the launching entry points then fail with
+ * KFA_CUDA_ERROR and a message that says so, rather than breaking the capture).  Idempotent.
+ * (No counterpart in the reference, whose host launcher allocates through PyTorch.)
+ */
+KFA_API int kfa_init(void);
+
+/*
  * Attention forward.  Replaces the module function `forward` of the reference's
  * host launcher (native.cpp:1034-1037, forward_canonical native.cpp:294-314).
  *
@@ -123,7 +133,9 @@ KFA_API int kfa_center_keys(const kfa_tensor* k, kfa_tensor* centered, void* wor
  *   - batch * heads * channels must not exceed kfa_center_keys_static_limit() (16384); larger
  *     problems return KFA_TOO_LARGE and launch nothing;
  *   - every GPU that loads the library holds the array (about 2.1 MB) until the process exits;
- *   - all calls share the array: calls that overlap in time on one GPU race with each other;
+ *   - shapes the one-launch thread-block-cluster kernel serves (64/128/256/512 channels, >= 64 rows,
+ *     16-byte addressable rows, slab fits in shared memory) need no scratch and leave the array alone;
+ *     all other calls share the array, and such calls that overlap in time on one GPU race with each other;
  *   - the first call on a device looks up the array's address; make it before any stream capture.
  */
 KFA_API size_t kfa_center_keys_static_limit(void);
@@ -163,6 +175,9 @@ KFA_API void kfa_clear_cache(void);
 
 /* Kernels launched by this library since load (all threads) - observability only. */
 KFA_API uint64_t kfa_launch_count(void);
+/* The same count per kernel family: entry `index` (0, 1, ...) gives a name such as "pipeline_forward" and
+ * its launches since load; returns non-zero once `index` is past the last name seen so far. */
+KFA_API int kfa_launch_stats(int index, char* name, size_t name_bytes, uint64_t* launches);
 
 /*
  * Per-kernel timing for benchmarks.  While enabled, every launch is bracketed by CUDA events
@@ -179,7 +194,10 @@ KFA_API void kfa_profile_reset(void);
 /*
  * Device-side status: 0 when no kernel reported a problem, otherwise the code a bounded
  * wait stored when it gave up.  Reading does not synchronise; call after the stream is
- * idle.  `reset` != 0 clears it.
+ * idle.  `reset` != 0 clears it.  While the status is non-zero every tensor-memory kernel
+ * skips its work, and kfa_forward, kfa_backward and the neighbourhood entry points return
+ * KFA_DEVICE_TIMEOUT without launching (so no caller is handed unwritten outputs); acknowledge
+ * the report with kfa_device_status(1) to resume.
  */
 KFA_API int kfa_device_status(int reset);
 

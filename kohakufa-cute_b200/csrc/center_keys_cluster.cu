@@ -8,6 +8,8 @@
 // bitwise reproducible.  (Reference behaviour: src/kohakufa_cute/api.py:100-103 of the reference project.)
 #include <cooperative_groups.h>
 
+#include <atomic>
+
 #include "kfa_common.cuh"
 #include "launchers.h"
 
@@ -128,6 +130,39 @@ bool center_keys_cluster_supported(const void* k, const void* out, int S, int D,
     const size_t rows_per_cta = ((size_t)S + kCluster - 1) / kCluster;
     const size_t bytes = rows_per_cta * D * 2 + (size_t)((kThreads / (D / 8)) * D + 2 * D) * sizeof(float);
     return bytes <= 200 * 1024;
+}
+
+// Whether a cluster of 8 CTAs with this much shared memory each can be resident on the current device at all
+// (a partitioned or smaller device may not manage).  Asked once per (device, type, shared-memory size class).
+bool center_keys_cluster_schedulable(bool bf16, int S, int D) {
+    static std::atomic<int> cache[64][2][2];  // 0 unknown, 1 yes, 2 no; [device][type][small/large shared memory]
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    const size_t rows_per_cta = ((size_t)S + kCluster - 1) / kCluster;
+    const size_t bytes = rows_per_cta * D * 2 + (size_t)((kThreads / (D / 8)) * D + 2 * D) * sizeof(float);
+    const int cls = bytes > 100 * 1024 ? 1 : 0;
+    const int seen = cache[dev][bf16 ? 1 : 0][cls].load();
+    if (seen) return seen == 1;
+    // ask for the larger size of the class, so that one answer covers every size in it
+    const size_t ask = cls ? 200 * 1024 : 100 * 1024;
+    const void* fn = bf16 ? (const void*)center_keys_cluster<__nv_bfloat16> : (const void*)center_keys_cluster<__half>;
+    int clusters = 0;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(kCluster);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = ask;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kCluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    bool ok = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ask) == cudaSuccess &&
+              cudaOccupancyMaxActiveClusters(&clusters, fn, &config) == cudaSuccess && clusters > 0;
+    if (!ok) cudaGetLastError();
+    cache[dev][bf16 ? 1 : 0][cls] = ok ? 1 : 2;
+    return ok;
 }
 
 cudaError_t launch_center_keys_cluster(const void* k, void* out, bool bf16, int B, int H, int S, int D,

@@ -458,8 +458,9 @@ template <typename T>
 __global__ void __launch_bounds__(256) column_partial(const T* k, float* partial, int H, int S, int D, int splits,
                                                       int64_t s0, int64_t s1, int64_t s2, int64_t s3) {
     __shared__ float part[8][33];
-    const int bh = blockIdx.y, b = bh / H, h = bh % H, split = blockIdx.z;
-    const int d = blockIdx.x * 32 + (threadIdx.x & 31);
+    // batch*head on grid.x (no 65535 limit there), channel block on grid.y, sequence split on grid.z
+    const int bh = blockIdx.x, b = bh / H, h = bh % H, split = blockIdx.z;
+    const int d = blockIdx.y * 32 + (threadIdx.x & 31);
     const int lane_s = threadIdx.x >> 5;
     const int rows_per = (S + splits - 1) / splits;
     const int r0 = split * rows_per, r1 = min(S, r0 + rows_per);
@@ -488,8 +489,11 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) subtract_mean(const T* k, const float* mean, T* out, int H, int S, int D,
                                                      int64_t s0, int64_t s1, int64_t s2, int64_t s3, int64_t o0,
                                                      int64_t o1, int64_t o2, int64_t o3) {
-    const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    const int bh = blockIdx.y, b = bh / H, h = bh % H;
+    // one-dimensional grid: `per_head` blocks per (batch, head)
+    const int64_t items = VEC ? (int64_t)S * (D / 8) : (int64_t)S * D;
+    const int64_t per_head = (items + 255) / 256;
+    const int bh = (int)(blockIdx.x / per_head), b = bh / H, h = bh % H;
+    const int64_t idx = (int64_t)(blockIdx.x % per_head) * 256 + threadIdx.x;
     if (VEC) {
         const int per_row = D / 8;
         if (idx >= (int64_t)S * per_row) return;
@@ -622,16 +626,26 @@ cudaError_t launch_general_backward(const AttnParams& p, bool bf16, int which, c
 
 // workspace: kMeanSplits * B*H*D partial sums followed by B*H*D means
 cudaError_t launch_center_keys(const void* k, void* out, float* workspace, bool bf16, int B, int H, int S, int D,
-                               const int64_t* ks, const int64_t* os, cudaStream_t st) {
-    // one launch over thread-block clusters when a head's slab fits in shared memory
-    if (center_keys_cluster_supported(k, out, S, D, ks, os))
-        return launch_center_keys_cluster(k, out, bf16, B, H, S, D, ks, os, st);
+                               const int64_t* ks, const int64_t* os, cudaStream_t st, int* launches) {
+    // one launch over thread-block clusters when a head's slab fits in shared memory and the device can
+    // co-schedule the cluster; a failed cluster launch (a partition that cannot) falls through as well
+    if (center_keys_cluster_supported(k, out, S, D, ks, os) && center_keys_cluster_schedulable(bf16, S, D)) {
+        if (launch_center_keys_cluster(k, out, bf16, B, H, S, D, ks, os, st) == cudaSuccess) {
+            if (launches) *launches = 1;
+            return cudaSuccess;
+        }
+        cudaGetLastError();
+    }
+    if (launches) *launches = 3;
     const int splits = max(1, min(kMeanSplits, S / 128));
     float* partial = workspace;
     float* mean = workspace + (int64_t)kMeanSplits * B * H * D;
     const bool vec = vector_ok(k, ks, D) && vector_ok(out, os, D);
     const int64_t items = vec ? (int64_t)S * (D / 8) : (int64_t)S * D;
-    dim3 g1((D + 31) / 32, B * H, splits), g3((unsigned)blocks_for(items, 256), B * H);
+    const int64_t sub_blocks = blocks_for(items, 256) * B * H;
+    if (sub_blocks > INT32_MAX) return cudaErrorInvalidConfiguration;
+    dim3 g1(B * H, (D + 31) / 32, splits);
+    const unsigned g3 = (unsigned)sub_blocks;
     if (bf16) {
         using T = __nv_bfloat16;
         column_partial<T><<<g1, 256, 0, st>>>((const T*)k, partial, H, S, D, splits, ks[0], ks[1], ks[2], ks[3]);

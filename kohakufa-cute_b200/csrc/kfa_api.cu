@@ -44,10 +44,50 @@ struct Total {
 };
 std::vector<Total> g_totals;
 
+// Launches per kernel name since load (observability: kfa_launch_stats).
+constexpr int kMaxStatNames = 48;
+struct LaunchStat {
+    std::atomic<const char*> name{nullptr};
+    std::atomic<uint64_t> launches{0};
+};
+LaunchStat g_launch_stats[kMaxStatNames];
+
+void count_kernel(const char* name, uint64_t n) {
+    g_launches += n;
+    for (int i = 0; i < kMaxStatNames; ++i) {
+        const char* seen = g_launch_stats[i].name.load(std::memory_order_acquire);
+        if (seen == nullptr) {
+            const char* expected = nullptr;
+            if (g_launch_stats[i].name.compare_exchange_strong(expected, name, std::memory_order_acq_rel)) seen = name;
+            else seen = expected;
+        }
+        if (seen == name || std::strcmp(seen, name) == 0) {
+            g_launch_stats[i].launches += n;
+            return;
+        }
+    }
+}
+
+#ifdef KFA_NVTX
+// Ranges around every launch for timeline tools (compile with -DKFA_NVTX; needs the toolkit's nvtx3 headers).
+}  // namespace
+#include <nvtx3/nvToolsExt.h>
+namespace {
+struct Range {
+    explicit Range(const char* name) { nvtxRangePushA(name); }
+    ~Range() { nvtxRangePop(); }
+};
+#else
+struct Range {
+    explicit Range(const char*) {}
+};
+#endif
+
 // Runs one launch; when profiling is on, brackets it with events.
 template <typename F>
 cudaError_t timed(const char* name, cudaStream_t st, F&& launch) {
-    g_launches += 1;
+    count_kernel(name, 1);
+    Range range(name);
     if (!g_profile_on.load(std::memory_order_relaxed)) return launch();
     Sample s{name, nullptr, nullptr};
     cudaEventCreate(&s.begin);
@@ -60,18 +100,18 @@ cudaError_t timed(const char* name, cudaStream_t st, F&& launch) {
     return e;
 }
 
-// A side stream with its fork/join events per caller stream (created on first use, kept for the process).
+// A side stream with its fork/join events per (host thread, device, caller stream), created on first use and
+// kept for the thread's lifetime.  Per thread, because two host threads that record the same event pair
+// (even on the same caller stream) would race on the records.
 struct Side {
     cudaStream_t stream = nullptr;
     cudaEvent_t fork = nullptr, join = nullptr;
 };
-std::mutex g_side_mutex;
-std::vector<std::pair<std::pair<int, cudaStream_t>, Side*>> g_sides;
+thread_local std::vector<std::pair<std::pair<int, cudaStream_t>, Side*>> g_sides;
 
 Side* side_stream_for(cudaStream_t user) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
-    std::lock_guard<std::mutex> lock(g_side_mutex);
     for (auto& entry : g_sides)
         if (entry.first.first == dev && entry.first.second == user) return entry.second;
     // creating a stream is not allowed while the caller's stream is being captured: stay on one stream then
@@ -100,7 +140,9 @@ int* g_status_dev[kMaxDevices] = {};
 int* g_abort_dev[kMaxDevices] = {};  // device memory: launch-wide abort flag (see AttnParams::abort_flag)
 std::mutex g_status_mutex;
 
-int* status_word(int* err) {
+// `st` is the stream the caller is about to launch on: the first call on a device allocates the status word
+// and the abort flag, which is not allowed while that stream is being captured.
+int* status_word(int* err, cudaStream_t st = nullptr) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
@@ -109,6 +151,14 @@ int* status_word(int* err) {
     }
     std::lock_guard<std::mutex> lock(g_status_mutex);
     if (!g_status_dev[dev]) {
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &capturing) != cudaSuccess) cudaGetLastError();
+        if (capturing != cudaStreamCaptureStatusNone) {
+            *err = fail(KFA_CUDA_ERROR,
+                        "the first call on a device sets up per-device state and cannot run under stream capture: "
+                        "call kfa_init() (or run one call) on this device before capturing");
+            return nullptr;
+        }
         int* host = nullptr;
         e = cudaHostAlloc(reinterpret_cast<void**>(&host), 64, cudaHostAllocMapped | cudaHostAllocPortable);
         if (e != cudaSuccess) {
@@ -141,6 +191,25 @@ int* abort_flag_of_current_device() {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
     std::lock_guard<std::mutex> lock(g_status_mutex);
     return g_abort_dev[dev];
+}
+
+// A bounded device-side wait that ran out leaves its code in the status word and keeps every later
+// tensor-memory launch idle; entry points refuse to launch (and to hand back unwritten outputs) until the
+// report is acknowledged with kfa_device_status(1).  Reading the mapped word is a plain host load.
+int check_device_ok() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    int* host = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_status_mutex);
+        host = g_status_host[dev];
+    }
+    if (!host) return 0;
+    const int code = *reinterpret_cast<volatile int*>(host);
+    if (code == 0) return 0;
+    return fail(KFA_DEVICE_TIMEOUT,
+                "a device-side wait of an earlier launch ran out (status %d); results since then are invalid. "
+                "Acknowledge with kfa_device_status(1) before launching again", code);
 }
 
 bool is_half_type(const kfa_tensor* t) { return t->dtype == KFA_F16 || t->dtype == KFA_BF16; }
@@ -181,7 +250,7 @@ int check_qkv(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v) {
 }
 
 int fill_common(kfa::AttnParams& p, const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v,
-                const kfa_tensor* mask, float scale, int causal) {
+                const kfa_tensor* mask, float scale, int causal, cudaStream_t st = nullptr) {
     std::memset(&p, 0, sizeof(p));
     p.q = q->data;
     p.k = k->data;
@@ -209,7 +278,7 @@ int fill_common(kfa::AttnParams& p, const kfa_tensor* q, const kfa_tensor* k, co
         p.has_mask = 1;
     }
     int err = 0;
-    p.status = status_word(&err);
+    p.status = status_word(&err, st);
     p.abort_flag = abort_flag_of_current_device();
     return err;
 }
@@ -275,7 +344,7 @@ int geometry(kfa::AttnParams& p, const int64_t* spatial, int nd, const int64_t* 
 
 namespace kfa {
 void note_failure(int code, const char* message) { fail(code, "%s", message); }
-void count_launches(int n) { g_launches += (uint64_t)n; }
+void count_launches(const char* name, int n) { count_kernel(name, (uint64_t)n); }
 }  // namespace kfa
 
 extern "C" {
@@ -285,6 +354,21 @@ int kfa_version(void) { return (0 << 16) | 1; }
 const char* kfa_last_error(void) { return g_error; }
 
 uint64_t kfa_launch_count(void) { return g_launches.load(); }
+
+int kfa_launch_stats(int index, char* name, size_t name_bytes, uint64_t* launches) {
+    if (index < 0 || index >= kMaxStatNames || !name || name_bytes == 0)
+        return fail(KFA_INVALID_ARGUMENT, "launch statistics entry %d does not exist", index);
+    const char* seen = g_launch_stats[index].name.load(std::memory_order_acquire);
+    if (!seen) return fail(KFA_INVALID_ARGUMENT, "launch statistics entry %d does not exist", index);
+    std::snprintf(name, name_bytes, "%s", seen);
+    if (launches) *launches = g_launch_stats[index].launches.load();
+    return 0;
+}
+
+int kfa_init(void) {
+    int err = 0;
+    return status_word(&err) ? 0 : err;
+}
 
 int kfa_cache_size(void) { return kfa::pipeline_configured_variants(); }
 
@@ -480,9 +564,10 @@ int kfa_selected_family(const kfa_tensor* q, const kfa_tensor* k, const kfa_tens
 int kfa_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
                 kfa_tensor* out, kfa_tensor* maximum, kfa_tensor* logsum, kfa_tensor* blocks, float scale,
                 int causal, void* stream) {
+    if (int e = check_device_ok()) return e;
     if (int e = check_qkv(q, k, v)) return e;
     kfa::AttnParams p;
-    if (int e = fill_common(p, q, k, v, mask, scale, causal)) return e;
+    if (int e = fill_common(p, q, k, v, mask, scale, causal, static_cast<cudaStream_t>(stream))) return e;
     if (int e = check_like(out, q, "out")) return e;
     if (!contiguous3(maximum, p.B, p.Hq, p.Sq) || !contiguous3(logsum, p.B, p.Hq, p.Sq))
         return fail(KFA_INVALID_ARGUMENT, "maximum/logsum must be contiguous float32 [B,Hq,Sq]");
@@ -546,9 +631,10 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
                  const kfa_tensor* out, const kfa_tensor* maximum, const kfa_tensor* logsum, const kfa_tensor* dout,
                  const kfa_tensor* blocks, kfa_tensor* dq, kfa_tensor* dk, kfa_tensor* dv, void* workspace,
                  size_t workspace_bytes, float scale, int causal, void* stream) {
+    if (int e = check_device_ok()) return e;
     if (int e = check_qkv(q, k, v)) return e;
     kfa::AttnParams p;
-    if (int e = fill_common(p, q, k, v, mask, scale, causal)) return e;
+    if (int e = fill_common(p, q, k, v, mask, scale, causal, static_cast<cudaStream_t>(stream))) return e;
     if (int e = check_like(out, q, "out")) return e;
     if (int e = check_like(dout, q, "dout")) return e;
     if (int e = check_like(dq, q, "dq")) return e;
@@ -667,27 +753,27 @@ int kfa_center_keys(const kfa_tensor* k, kfa_tensor* centered, void* workspace, 
         return fail(KFA_INVALID_ARGUMENT, "center_keys workspace too small");
     for (int i = 0; i < 4; ++i)
         if (k->sizes[i] <= 0 || k->sizes[i] > INT32_MAX) return fail(KFA_INVALID_ARGUMENT, "center_keys: bad extent");
-    if (k->sizes[0] * k->sizes[1] > 65535) return fail(KFA_TOO_LARGE, "center_keys: batch*heads exceeds 65535");
+    if (k->sizes[0] * k->sizes[1] > INT32_MAX / 8) return fail(KFA_TOO_LARGE, "center_keys: batch*heads exceeds 2^28");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int launches = 0;
     cudaError_t ce = timed("center_keys", st, [&] {
         return kfa::launch_center_keys(k->data, centered->data, static_cast<float*>(workspace), k->dtype == KFA_BF16,
                                        (int)k->sizes[0], (int)k->sizes[1], (int)k->sizes[2], (int)k->sizes[3],
-                                       k->strides, centered->strides, st);
+                                       k->strides, centered->strides, st, &launches);
     });
     if (ce != cudaSuccess) return cuda_fail(ce, "center_keys launch");
-    // the one-launch cluster kernel, or three kernels (partial sums, means, subtraction)
-    if (!kfa::center_keys_cluster_supported(k->data, centered->data, (int)k->sizes[2], (int)k->sizes[3], k->strides,
-                                            centered->strides))
-        g_launches += 2;
+    // one launch (thread-block clusters) or three (partial sums, means, subtraction)
+    if (launches > 1) count_kernel("center_keys", (uint64_t)(launches - 1));
     return 0;
 }
 
 int kfa_neighborhood_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, kfa_tensor* out,
                              kfa_tensor* maximum, kfa_tensor* logsum, const int64_t* spatial, int nd,
                              const int64_t* window, float scale, void* stream) {
+    if (int e = check_device_ok()) return e;
     if (int e = check_qkv(q, k, v)) return e;
     kfa::AttnParams p;
-    if (int e = fill_common(p, q, k, v, nullptr, scale, 0)) return e;
+    if (int e = fill_common(p, q, k, v, nullptr, scale, 0, static_cast<cudaStream_t>(stream))) return e;
     if (int e = geometry(p, spatial, nd, window)) return e;
     if (int e = check_like(out, q, "out")) return e;
     if (!contiguous3(maximum, p.B, p.Hq, p.Sq) || !contiguous3(logsum, p.B, p.Hq, p.Sq))
@@ -717,9 +803,10 @@ int kfa_neighborhood_backward(const kfa_tensor* q, const kfa_tensor* k, const kf
                               const kfa_tensor* maximum, const kfa_tensor* logsum, const kfa_tensor* dout,
                               kfa_tensor* dq, kfa_tensor* dk, kfa_tensor* dv, void* workspace, size_t workspace_bytes,
                               const int64_t* spatial, int nd, const int64_t* window, float scale, void* stream) {
+    if (int e = check_device_ok()) return e;
     if (int e = check_qkv(q, k, v)) return e;
     kfa::AttnParams p;
-    if (int e = fill_common(p, q, k, v, nullptr, scale, 0)) return e;
+    if (int e = fill_common(p, q, k, v, nullptr, scale, 0, static_cast<cudaStream_t>(stream))) return e;
     if (int e = geometry(p, spatial, nd, window)) return e;
     if (int e = check_like(out, q, "out")) return e;
     if (int e = check_like(dout, q, "dout")) return e;

@@ -13,8 +13,11 @@
 //     are rejected with KFA_TOO_LARGE; nothing is launched;
 //   * the array keeps whatever the previous call left in it.  The kernels overwrite every element
 //     they later read, so nothing has to be cleared between calls;
-//   * two calls that overlap in time on the same GPU (different streams or threads) race on the
-//     array: serialise them, or use kfa_center_keys with caller-owned scratch;
+//   * shapes the one-launch thread-block-cluster kernel serves (64/128/256/512 channels, at least 64 rows,
+//     16-byte addressable rows, a sequence slab that fits in shared memory) need no scratch and do not
+//     touch the array; every other shape runs the three-kernel path through it;
+//   * two calls of the second kind that overlap in time on the same GPU (different streams or threads)
+//     race on the array: serialise them, or use kfa_center_keys with caller-owned scratch;
 //   * the first call on each device looks up the array's device address (with that device
 //     current).  Make that first call before starting any stream capture on the device.
 #include "../../include/kfa.h"
@@ -26,7 +29,7 @@
 
 namespace kfa {
 void note_failure(int code, const char* message);  // records the thread's last error (kfa_api.cu)
-void count_launches(int n);
+void count_launches(const char* name, int n);
 }  // namespace kfa
 
 namespace {
@@ -89,7 +92,7 @@ int kfa_center_keys_static(const kfa_tensor* k, kfa_tensor* centered, void* stre
         }
     }
     const size_t units = (size_t)k->sizes[0] * k->sizes[1] * k->sizes[3];
-    if (units > kMaxUnits || k->sizes[0] * k->sizes[1] > 65535) {
+    if (units > kMaxUnits) {
         char text[200];
         std::snprintf(text, sizeof(text),
                       "kfa_center_keys_static: batch*heads*channels = %zu exceeds the fixed scratch capacity %zu "
@@ -101,14 +104,17 @@ int kfa_center_keys_static(const kfa_tensor* k, kfa_tensor* centered, void* stre
     int error = 0;
     float* scratch = scratch_address(&error);
     if (!scratch) return error;
+    int launches = 0;
     cudaError_t ce = kfa::launch_center_keys(k->data, centered->data, scratch, k->dtype == KFA_BF16, (int)k->sizes[0],
                                              (int)k->sizes[1], (int)k->sizes[2], (int)k->sizes[3], k->strides,
-                                             centered->strides, static_cast<cudaStream_t>(stream));
+                                             centered->strides, static_cast<cudaStream_t>(stream), &launches);
     if (ce != cudaSuccess) {
         kfa::note_failure(KFA_CUDA_ERROR, cudaGetErrorString(ce));
         return KFA_CUDA_ERROR;
     }
-    kfa::count_launches(3);
+    // one kernel when the shape suits the thread-block-cluster kernel (which needs no scratch at all),
+    // three when the partial sums and means go through the static array
+    kfa::count_launches("center_keys_static", launches);
     return 0;
 }
 

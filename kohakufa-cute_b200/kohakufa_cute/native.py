@@ -45,6 +45,7 @@ _I64P = ctypes.POINTER(ctypes.c_int64)
 SIGNATURES = {
     "kfa_version": (ctypes.c_int, []),
     "kfa_last_error": (ctypes.c_char_p, []),
+    "kfa_init": (ctypes.c_int, []),
     "kfa_forward": (ctypes.c_int, [_TP, _TP, _TP, _TP, _TP, _TP, _TP, _TP, ctypes.c_float, ctypes.c_int,
                                    ctypes.c_void_p]),
     "kfa_pack_mask": (ctypes.c_int, [_TP, _TP, ctypes.c_void_p]),
@@ -64,6 +65,8 @@ SIGNATURES = {
     "kfa_cache_size": (ctypes.c_int, []),
     "kfa_clear_cache": (None, []),
     "kfa_launch_count": (ctypes.c_uint64, []),
+    "kfa_launch_stats": (ctypes.c_int, [ctypes.c_int, ctypes.c_char_p, ctypes.c_size_t,
+                                        ctypes.POINTER(ctypes.c_uint64)]),
     "kfa_device_status": (ctypes.c_int, [ctypes.c_int]),
     "kfa_profile_enable": (None, [ctypes.c_int]),
     "kfa_profile_collect": (ctypes.c_int, []),
@@ -127,7 +130,13 @@ def _check(code):
     message = library().kfa_last_error().decode()
     if code == 1:
         raise ValueError(message)
+    if code == 3:
+        raise DeviceTimeoutError(message)
     raise RuntimeError(f"libkfa error {code}: {message}")
+
+
+class DeviceTimeoutError(RuntimeError):
+    """A bounded device-side wait ran out earlier; acknowledge with ``device_status(reset=True)``."""
 
 
 def _stream(device):
@@ -303,6 +312,25 @@ def clear_cache():
 
 def launch_count():
     return int(library().kfa_launch_count())
+
+
+def launch_stats():
+    """{kernel family name: launches since load} (``kfa_launch_stats``)."""
+    lib = library()
+    result, index = {}, 0
+    while True:
+        name, launches = ctypes.create_string_buffer(64), ctypes.c_uint64()
+        if lib.kfa_launch_stats(index, name, 64, ctypes.byref(launches)) != 0:
+            return result
+        result[name.value.decode()] = int(launches.value)
+        index += 1
+
+
+def init(device=None):
+    """Per-device set-up (``kfa_init``); needed explicitly only when the first call on a device would
+    otherwise happen inside a CUDA-graph capture."""
+    with torch.cuda.device(torch.cuda.current_device() if device is None else device):
+        _check(library().kfa_init())
 
 
 def device_status(reset=False):

@@ -18,6 +18,9 @@ project):
                              the kernel actually produced feeding delta,
                              ``benchmarks/reference.py:95-138`` and
                              ``docs/precision.md:13-23``
+* ``contract_columns``     – the same contract for chosen key rows only (dK, dV of long
+                             sequences), streamed over query chunks; the column-restricted
+                             evaluation idea of ``benchmarks/neighborhood/key_precision_reference.py:73-149``
 * ``forward_statistics``   – the two saved row statistics (unscaled signed
                              row maximum, base-2 log of the normaliser),
                              ``src/kohakufa_cute/kernels.py:1286-1333,1729-1742``
@@ -41,6 +44,7 @@ __all__ = [
     "visible_pairs",
     "math_reference",
     "contract_reference",
+    "contract_columns",
     "forward_statistics",
     "center_keys",
     "center_keys_backward",
@@ -209,6 +213,60 @@ def contract_reference(inputs, dout, mask=None, causal=False, scale=None, *, out
             dk[b, kv] += (ds_low.T @ qh.double()) * scale
             dv[b, kv] += p_low.double().T @ gh.double()
     return out, dq, dk, dv
+
+
+@torch.no_grad()
+def contract_columns(inputs, dout, mask=None, causal=False, scale=None, *, output, key_rows, chunk=2048):
+    """``dk`` and ``dv`` of the rounding contract for the key rows ``key_rows`` only (float64,
+    ``[B, Hkv, len(key_rows), D]``), complete over all queries.
+
+    Queries are processed in chunks: each chunk forms its full score rows (for the row maximum and the
+    normaliser, exactly as ``contract_reference``) but keeps P and dS only at the chosen columns, so the
+    memory stays ``chunk x Sk`` whatever the sequence length.  ``output`` is the rounded forward output.
+    """
+    q, k, v = (t.detach().cpu() for t in inputs)
+    g, given = dout.detach().cpu(), output.detach().cpu()
+    dtype = q.dtype
+    scale = _default_scale(q, scale)
+    sign = 1.0 if scale >= 0 else -1.0
+    group = _heads(q, k)
+    B, Hq, Sq, D = q.shape
+    Sk = k.shape[2]
+    cols = torch.as_tensor(key_rows, dtype=torch.long)
+    dk = torch.zeros(B, k.shape[1], cols.numel(), D, dtype=torch.float64)
+    dv = torch.zeros_like(dk)
+    m4 = None
+    if mask is not None:
+        m4 = mask.cpu()
+        while m4.dim() < 4:
+            m4 = m4.unsqueeze(0)
+        m4 = m4.expand(B, Hq, Sq, Sk)
+    key_index = torch.arange(Sk).view(1, Sk)
+    for b in range(B):
+        for h in range(Hq):
+            kv = h // group
+            kf, vc = k[b, kv].float(), v[b, kv, cols].float()
+            for r0 in range(0, Sq, chunk):
+                r1 = min(Sq, r0 + chunk)
+                qh, gh = q[b, h, r0:r1], g[b, h, r0:r1]
+                seen = torch.ones(r1 - r0, Sk, dtype=torch.bool)
+                if causal:
+                    seen &= key_index <= torch.arange(r0, r1).view(-1, 1)
+                if m4 is not None:
+                    seen &= m4[b, h, r0:r1]
+                alive = seen.any(-1, keepdim=True)
+                s = (qh.float() @ kf.T).double() * sign
+                s = s.masked_fill(~seen, -math.inf)
+                m = s.amax(-1, keepdim=True).masked_fill(~alive, 0.0)
+                total = torch.exp((s - m) * abs(scale)).masked_fill(~seen, 0.0).sum(-1, keepdim=True).masked_fill(~alive, 1.0)
+                p = (torch.exp((s[:, cols] - m) * abs(scale)).masked_fill(~seen[:, cols], 0.0)) / total
+                dp = gh.float() @ vc.T
+                delta = (given[b, h, r0:r1].float() * gh.float()).sum(-1, keepdim=True)
+                p_low = p.float().to(dtype).float()
+                ds_low = (p_low * (dp - delta)).to(dtype).double()
+                dk[b, kv] += (ds_low.T @ qh.double()) * scale
+                dv[b, kv] += p_low.double().T @ gh.double()
+    return dk, dv
 
 
 def center_keys(k):

@@ -17,6 +17,10 @@ Reference locations restated here (paths inside the reference project):
                            ``benchmarks/neighborhood/key_precision_reference.py:17-69`` with
                            ``precision_reference.py:15-57``; described in ``docs/precision.md:46-80``
 * 3-D two-term forward   – ``benchmarks/neighborhood/reference.py:47-69``
+* sampled evaluation     – ``na_contract_sampled`` evaluates the same contract on chosen query rows (out, dQ)
+                           and chosen key rows (dK, dV) only, so that grids of benchmark size can be checked;
+                           the sampling protocol follows ``docs/neighborhood/reports/3d-multigpu.md:41`` and
+                           the column-restricted idea of ``benchmarks/neighborhood/key_precision_reference.py:73-149``
 
 Tokens are flattened row-major with the last spatial axis fastest.
 """
@@ -38,6 +42,8 @@ __all__ = [
     "na_math_reference",
     "na_contract_reference",
     "na_two_term_forward",
+    "window_indices",
+    "na_contract_sampled",
 ]
 
 
@@ -149,3 +155,93 @@ def na_two_term_forward(inputs, spatial, window, scale):
     lo = (w - hi).to(q.dtype).float()
     num = hi.double() @ v.double() + lo.double() @ v.double()
     return num / w.sum(-1, keepdim=True).double()
+
+
+def window_indices(spatial, window, rows):
+    """``[len(rows), prod(window)]`` flattened key indices attended to by the given flattened queries."""
+    spatial, window = tuple(int(x) for x in spatial), tuple(int(x) for x in window)
+    rows = torch.as_tensor(rows, dtype=torch.long)
+    pitch = [math.prod(spatial[a + 1:]) for a in range(len(spatial))]
+    rest = rows.clone()
+    keys = torch.zeros(rows.numel(), 1, dtype=torch.long)
+    for extent, w, stride in zip(spatial, window, pitch):
+        coord = rest // stride
+        rest = rest % stride
+        first = (coord - w // 2).clamp(0, extent - w)
+        axis = (first[:, None] + torch.arange(w)[None, :]) * stride  # [n, w]
+        keys = (keys[:, :, None] + axis[:, None, :]).reshape(rows.numel(), -1)
+    return keys
+
+
+def _queries_seeing(spatial, window, key):
+    """Flattened indices of all queries whose window contains the flattened key index."""
+    pitch = [math.prod(spatial[a + 1:]) for a in range(len(spatial))]
+    ranges, rest = [], int(key)
+    for extent, w, stride in zip(spatial, window, pitch):
+        lo, hi = inverse_axis_range(rest // stride, extent, w)
+        ranges.append(range(lo, hi + 1))
+        rest %= stride
+    return [sum(c * s for c, s in zip(coords, pitch)) for coords in itertools.product(*ranges)]
+
+
+@torch.no_grad()
+def na_contract_sampled(inputs, dout, spatial, window, scale, output, query_rows, key_rows, two_term=False):
+    """The contract of ``na_contract_reference`` evaluated sparsely.
+
+    Returns ``(out, dq, dk, dv)`` in float64 where ``out``/``dq`` hold the rows ``query_rows`` and
+    ``dk``/``dv`` the rows ``key_rows`` (each complete: every query that sees a sampled key contributes).
+    ``out`` is the plain FP64 product, or the two-term product of the 3-D forward when ``two_term``.
+    """
+    q, k, v = (t.detach().cpu() for t in inputs)
+    g, o_given = dout.detach().cpu(), output.detach().cpu()
+    dtype = q.dtype
+    spatial, window = tuple(int(x) for x in spatial), tuple(int(x) for x in window)
+    query_rows = torch.as_tensor(query_rows, dtype=torch.long)
+    key_rows = [int(x) for x in key_rows]
+    seeing = {c: _queries_seeing(spatial, window, c) for c in key_rows}
+    extra = sorted({r for rows in seeing.values() for r in rows})
+    rows = torch.unique(torch.cat([query_rows, torch.tensor(extra, dtype=torch.long)]))
+    place = {int(r): n for n, r in enumerate(rows.tolist())}
+    idx = window_indices(spatial, window, rows)  # [n, W]
+    B, H, _, D = q.shape
+    nq, nk = query_rows.numel(), len(key_rows)
+    out = torch.zeros(B, H, nq, D, dtype=torch.float64)
+    dq = torch.zeros(B, H, nq, D, dtype=torch.float64)
+    dk = torch.zeros(B, H, nk, D, dtype=torch.float64)
+    dv = torch.zeros(B, H, nk, D, dtype=torch.float64)
+    qsel = torch.tensor([place[int(r)] for r in query_rows.tolist()], dtype=torch.long)
+    for b in range(B):
+        for h in range(H):
+            qr, gr = q[b, h, rows], g[b, h, rows]
+            kw, vw = k[b, h][idx], v[b, h][idx]  # [n, W, D]
+            s = torch.bmm(kw.float(), qr.float()[:, :, None])[:, :, 0].double()
+            dp = torch.bmm(vw.float(), gr.float()[:, :, None])[:, :, 0]
+            if scale < 0:
+                s = -s
+            w = torch.exp((s - s.amax(-1, keepdim=True)) * abs(scale))
+            p = w / w.sum(-1, keepdim=True)
+            p32 = p.float()
+            p_low = p32.to(dtype).float()
+            delta = (o_given[b, h, rows].float() * gr.float()).sum(-1, keepdim=True)
+            res = dp - delta
+            ds_q = (p32 * res).to(dtype).double()
+            kd, vd = kw.double(), vw.double()
+            key_mean = torch.einsum("nw,nwd->nd", p_low.double(), kd) / p_low.double().sum(-1, keepdim=True)
+            dq_all = (torch.einsum("nw,nwd->nd", ds_q, kd) - ds_q.sum(-1, keepdim=True) * key_mean) * scale
+            if two_term:
+                w32 = w.float()
+                hi = w32.to(dtype).float()
+                lo = (w32 - hi).to(dtype).float()
+                out_all = (torch.einsum("nw,nwd->nd", hi.double(), vd) + torch.einsum("nw,nwd->nd", lo.double(), vd)) \
+                    / w32.sum(-1, keepdim=True).double()
+            else:
+                out_all = torch.einsum("nw,nwd->nd", p, vd)
+            out[b, h], dq[b, h] = out_all[qsel], dq_all[qsel]
+            t = (p32 * res).sum(-1, keepdim=True) / p32.sum(-1, keepdim=True)
+            ds_k = (p32 * (res - t)).to(dtype).double()
+            for n, c in enumerate(key_rows):
+                members = torch.tensor([place[r] for r in seeing[c]], dtype=torch.long)
+                slot = (idx[members] == c).double()  # [m, W], one hit per row
+                dk[b, h, n] = ((ds_k[members] * slot).sum(-1, keepdim=True) * qr[members].double()).sum(0) * scale
+                dv[b, h, n] = ((p_low[members].double() * slot).sum(-1, keepdim=True) * gr[members].double()).sum(0)
+    return out, dq, dk, dv

@@ -21,11 +21,16 @@ def test_bounded_wait_runs_out_is_reported_and_cleared():
     assert 0 < skipped < ctas
     assert native.device_status(reset=False) == 9001
 
-    # until the condition is acknowledged the tensor-memory kernels skip their work and say so
+    # until the condition is acknowledged no entry point launches (nobody is handed unwritten outputs)
     q, k, v, dout = make_inputs(1, 2, 2, 256, 256, 128, torch.bfloat16, seed=91)
-    kohakufa_cute.attention(q, k, v, causal=True)
-    torch.cuda.synchronize()
-    assert native.device_status(reset=True) == 9001  # skipped CTAs do not overwrite the first report
+    before = native.launch_count()
+    with pytest.raises(native.DeviceTimeoutError, match="ran out"):
+        kohakufa_cute.attention(q, k, v, causal=True)
+    with pytest.raises(native.DeviceTimeoutError):
+        kohakufa_cute.neighborhood_attention(q[..., :64].contiguous(), k[..., :64].contiguous(), v[..., :64].contiguous(),
+                                             spatial_shape=(16, 16), window_size=3)
+    assert native.launch_count() == before
+    assert native.device_status(reset=True) == 9001
 
     # acknowledged: the same call works and matches the oracle
     out = kohakufa_cute.attention(q, k, v, causal=True)
