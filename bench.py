@@ -75,7 +75,8 @@ GEMM_SHARE = {"pipeline_forward": (2.0, 2), "general_forward": (2.0, 2), "neighb
               "wide_scores_ds": (1.0, 1), "wide_grad": (3.0, 3)}
 # DRAM bytes (read + write) per launch of the pipeline kernels on `llm_gqa`, scaled x4 from the ncu capture of
 # `llm_gqa_small` (a quarter of the batch x heads; traffic grows with the units): profiles/pipeline_kernels_llm_gqa_small_ncu.md
-NCU_TRAFFIC = {"llm_gqa": {"pipeline_forward": None, "pipeline_backward_q": None, "pipeline_backward_kv": None}}
+NCU_TRAFFIC = {"llm_gqa": {"pipeline_forward": 4 * (50.42e6 + 5.32e6), "pipeline_backward_q": 4 * (85.51e6 + 11.51e6),
+                           "pipeline_backward_kv": 4 * (88.05e6 + 4.82e6)}}
 
 
 def algorithmic_flops(w):

@@ -82,6 +82,9 @@ KFA_API int kfa_init(void);
  *   blocks   int32 tile table [Bm,Hm,ceil(Sq/64) or 1,ceil(Sk/64) or 1] written when mask != NULL
  *            (extent 1 on the mask's stride-0 axes); NULL when mask == NULL
  * A row with no visible key yields out = 0, maximum = -inf, logsum = 0.
+ * `maximum` and `logsum` may both be NULL: the statistics exist for the backward pass, and a forward
+ * call that nobody will differentiate (inference; the reference lists this mode as an open item,
+ * results/README.md:120-129) then writes the output only.
  */
 KFA_API int kfa_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
                 kfa_tensor* out, kfa_tensor* maximum, kfa_tensor* logsum, kfa_tensor* blocks, float scale,
@@ -167,6 +170,19 @@ KFA_API int kfa_neighborhood_backward(const kfa_tensor* q, const kfa_tensor* k, 
 KFA_API int kfa_merge_partial(kfa_tensor* acc_out, kfa_tensor* acc_maximum, kfa_tensor* acc_logsum,
                       const kfa_tensor* part_out, const kfa_tensor* part_maximum,
                       const kfa_tensor* part_logsum, float scale, void* stream);
+
+/*
+ * Merge step of a forward pass split over the key axis (short query sequences against long key
+ * sequences, where one CTA per head would leave the GPU idle): the caller runs kfa_forward on `splits`
+ * key ranges and this call folds the partial results, with the arithmetic of the reference's split
+ * forward (split_forward.py:219-245): out = sum_i w_i O_i / sum_i w_i with
+ * w_i = 2^((m_i - m) |scale| log2e + logsum_i), m = max_i m_i; the merged statistics describe the whole
+ * key range, so the ordinary backward applies.
+ *   out [B,H,S,D] 16-bit (any strides); maximum, logsum [B,H,S] f32 or both NULL;
+ *   part_out [splits,B,H,S,D] 16-bit contiguous; part_maximum, part_logsum [splits,B,H,S] f32 contiguous
+ */
+KFA_API int kfa_merge_splits(kfa_tensor* out, kfa_tensor* maximum, kfa_tensor* logsum, const kfa_tensor* part_out,
+                     const kfa_tensor* part_maximum, const kfa_tensor* part_logsum, float scale, void* stream);
 
 /* Number of kernel variants configured so far / forget them.  Replace `cache_size`
  * and `clear_cache` (native.cpp:1055-1065). */

@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(kWarps * 32) general_forward(AttnParams p) {
             const int d = 2 * (lane + 32 * i);
             if (d < D) store2<T, VEC>(orow, p.os[3], d, D, acc[r][i][0] / den, acc[r][i][1] / den);
         }
-        if (lane == 0) {
+        if (lane == 0 && p.maximum) {
             const int64_t si = ((int64_t)b * p.Hq + h) * p.Sq + row;
             p.maximum[si] = m[r];
             p.logsum[si] = log2f(den);
@@ -548,6 +548,42 @@ __global__ void __launch_bounds__(128) merge_partial(float* acc, float* am, floa
     }
 }
 
+// Merges the partial results of a forward pass split over the key axis: `splits` normalised outputs with their
+// (maximum, logsum) pairs -> one output row, rounded once, and the statistics of the whole key range.
+// part is [splits, rows, D] (16-bit, contiguous), pm / pl are [splits, rows].
+template <typename T>
+__global__ void __launch_bounds__(128) merge_splits(T* out, float* maximum, float* logsum, const T* part, const float* pm,
+                                                    const float* pl, int splits, int64_t rows, int D, float c2,
+                                                    int64_t o_b, int64_t o_h, int64_t o_s, int64_t o_d, int H, int S) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int s = (int)(row % S), h = (int)((row / S) % H), b = (int)(row / ((int64_t)S * H));
+    float m = -INFINITY;
+    for (int i = 0; i < splits; ++i) m = fmaxf(m, pm[(int64_t)i * rows + row]);
+    float total = 0.f;
+    for (int i = 0; i < splits; ++i) {
+        const float mi = pm[(int64_t)i * rows + row];
+        if (mi != -INFINITY) total += fast_ex2((mi - m) * c2 + pl[(int64_t)i * rows + row]);
+    }
+    const float inv = total > 0.f ? 1.f / total : 0.f;
+    T* orow = out + (int64_t)b * o_b + (int64_t)h * o_h + (int64_t)s * o_s;
+    for (int d = lane; d < D; d += 32) {
+        float acc = 0.f;
+        for (int i = 0; i < splits; ++i) {
+            const float mi = pm[(int64_t)i * rows + row];
+            if (mi == -INFINITY) continue;
+            const float w = fast_ex2((mi - m) * c2 + pl[(int64_t)i * rows + row]);
+            acc += w * to_float<T>(part[((int64_t)i * rows + row) * D + d]);
+        }
+        orow[(int64_t)d * o_d] = from_float<T>(acc * inv);
+    }
+    if (lane == 0 && maximum) {
+        maximum[row] = m;
+        logsum[row] = total > 0.f ? log2f(total) : 0.f;
+    }
+}
+
 inline int64_t blocks_for(int64_t items, int per_block) { return (items + per_block - 1) / per_block; }
 
 template <typename T, bool VEC>
@@ -659,6 +695,21 @@ cudaError_t launch_center_keys(const void* k, void* out, float* workspace, bool 
         if (vec) subtract_mean<T, true><<<g3, 256, 0, st>>>((const T*)k, mean, (T*)out, H, S, D, ks[0], ks[1], ks[2], ks[3], os[0], os[1], os[2], os[3]);
         else subtract_mean<T, false><<<g3, 256, 0, st>>>((const T*)k, mean, (T*)out, H, S, D, ks[0], ks[1], ks[2], ks[3], os[0], os[1], os[2], os[3]);
     }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_merge_splits(void* out, float* maximum, float* logsum, const void* part, const float* pm,
+                                const float* pl, bool bf16, int splits, int B, int H, int S, int D, const int64_t* os,
+                                float scale, cudaStream_t st) {
+    const int64_t rows = (int64_t)B * H * S;
+    const float c2 = fabsf(scale) * kLog2e;
+    const unsigned grid = (unsigned)blocks_for(rows, 4);
+    if (bf16)
+        merge_splits<__nv_bfloat16><<<grid, 128, 0, st>>>((__nv_bfloat16*)out, maximum, logsum, (const __nv_bfloat16*)part,
+                                                          pm, pl, splits, rows, D, c2, os[0], os[1], os[2], os[3], H, S);
+    else
+        merge_splits<__half><<<grid, 128, 0, st>>>((__half*)out, maximum, logsum, (const __half*)part, pm, pl, splits, rows,
+                                                   D, c2, os[0], os[1], os[2], os[3], H, S);
     return cudaGetLastError();
 }
 

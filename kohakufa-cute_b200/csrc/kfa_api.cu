@@ -569,13 +569,15 @@ int kfa_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, c
     kfa::AttnParams p;
     if (int e = fill_common(p, q, k, v, mask, scale, causal, static_cast<cudaStream_t>(stream))) return e;
     if (int e = check_like(out, q, "out")) return e;
-    if (!contiguous3(maximum, p.B, p.Hq, p.Sq) || !contiguous3(logsum, p.B, p.Hq, p.Sq))
-        return fail(KFA_INVALID_ARGUMENT, "maximum/logsum must be contiguous float32 [B,Hq,Sq]");
+    // both statistics, or neither (a forward pass nobody will differentiate keeps none)
+    const bool keep_statistics = maximum != nullptr || logsum != nullptr;
+    if (keep_statistics && (!contiguous3(maximum, p.B, p.Hq, p.Sq) || !contiguous3(logsum, p.B, p.Hq, p.Sq)))
+        return fail(KFA_INVALID_ARGUMENT, "maximum/logsum must be contiguous float32 [B,Hq,Sq] (or both NULL)");
     if (int e = bind_blocks(p, blocks)) return e;
     p.out = out->data;
     copy4(p.os, out->strides);
-    p.maximum = static_cast<float*>(maximum->data);
-    p.logsum = static_cast<float*>(logsum->data);
+    p.maximum = keep_statistics ? static_cast<float*>(maximum->data) : nullptr;
+    p.logsum = keep_statistics ? static_cast<float*>(logsum->data) : nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool bf16 = q->dtype == KFA_BF16;
     cudaError_t ce;
@@ -850,6 +852,39 @@ int kfa_neighborhood_backward(const kfa_tensor* q, const kfa_tensor* k, const kf
     if (ce != cudaSuccess) return cuda_fail(ce, "neighborhood backward (dQ) launch");
     ce = timed("neighborhood_backward_kv", st, [&] { return kfa::launch_neighborhood_backward(p, bf16, 1, st); });
     if (ce != cudaSuccess) return cuda_fail(ce, "neighborhood backward (dK/dV) launch");
+    return 0;
+}
+
+int kfa_merge_splits(kfa_tensor* out, kfa_tensor* maximum, kfa_tensor* logsum, const kfa_tensor* part_out,
+                     const kfa_tensor* part_maximum, const kfa_tensor* part_logsum, float scale, void* stream) {
+    if (!out || !out->data || out->ndim != 4 || !is_half_type(out))
+        return fail(KFA_INVALID_ARGUMENT, "merge_splits requires a 4D FP16/BF16 output");
+    if (!part_out || !part_out->data || part_out->ndim != 5 || part_out->dtype != out->dtype)
+        return fail(KFA_INVALID_ARGUMENT, "merge_splits requires [splits,B,H,S,D] partial outputs of the output's type");
+    const int64_t P = part_out->sizes[0], B = out->sizes[0], H = out->sizes[1], S = out->sizes[2], D = out->sizes[3];
+    if (P < 1 || P > 1024 || part_out->sizes[1] != B || part_out->sizes[2] != H || part_out->sizes[3] != S ||
+        part_out->sizes[4] != D || part_out->strides[4] != 1 || part_out->strides[3] != D ||
+        part_out->strides[2] != S * D || part_out->strides[1] != H * S * D || part_out->strides[0] != B * H * S * D)
+        return fail(KFA_INVALID_ARGUMENT, "merge_splits requires contiguous [splits,B,H,S,D] partial outputs");
+    auto stats_ok = [&](const kfa_tensor* t) {
+        return t && t->data && t->dtype == KFA_F32 && t->ndim == 4 && t->sizes[0] == P && t->sizes[1] == B &&
+               t->sizes[2] == H && t->sizes[3] == S && t->strides[3] == 1 && t->strides[2] == S &&
+               t->strides[1] == H * S && t->strides[0] == B * H * S;
+    };
+    if (!stats_ok(part_maximum) || !stats_ok(part_logsum))
+        return fail(KFA_INVALID_ARGUMENT, "merge_splits requires contiguous float32 [splits,B,H,S] partial statistics");
+    const bool keep = maximum != nullptr || logsum != nullptr;
+    if (keep && (!contiguous3(maximum, B, H, S) || !contiguous3(logsum, B, H, S)))
+        return fail(KFA_INVALID_ARGUMENT, "maximum/logsum must be contiguous float32 [B,H,S] (or both NULL)");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t ce = timed("merge_splits", st, [&] {
+        return kfa::launch_merge_splits(out->data, keep ? static_cast<float*>(maximum->data) : nullptr,
+                                        keep ? static_cast<float*>(logsum->data) : nullptr, part_out->data,
+                                        static_cast<const float*>(part_maximum->data),
+                                        static_cast<const float*>(part_logsum->data), out->dtype == KFA_BF16, (int)P,
+                                        (int)B, (int)H, (int)S, (int)D, out->strides, scale, st);
+    });
+    if (ce != cudaSuccess) return cuda_fail(ce, "merge_splits launch");
     return 0;
 }
 

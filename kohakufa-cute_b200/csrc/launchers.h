@@ -22,6 +22,10 @@ cudaError_t launch_merge_partial(float* acc, float* am, float* al, const void* p
                                  bool bf16, int B, int H, int S, int D, const int64_t* ps, float scale,
                                  cudaStream_t st);
 
+cudaError_t launch_merge_splits(void* out, float* maximum, float* logsum, const void* part, const float* pm,
+                                const float* pl, bool bf16, int splits, int B, int H, int S, int D, const int64_t* os,
+                                float scale, cudaStream_t st);
+
 cudaError_t launch_neighborhood_forward(const AttnParams& p, bool bf16, cudaStream_t st);
 cudaError_t launch_neighborhood_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st);
 

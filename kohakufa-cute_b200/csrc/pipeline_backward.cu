@@ -158,7 +158,8 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward_q(const __grid_
     if (warp == kRoleWarp) tmem_dealloc(tmem, 512);
 }
 
-// delta[row] = sum_d O * dO with coalesced 16-byte loads: D/8 threads per row.
+// delta[row] = sum_d O * dO with coalesced 16-byte loads: D/8 threads per row (D = 64 or 128 covers the
+// head's p.D channels; the threads beyond them add zero).
 template <typename T, int D>
 __global__ void __launch_bounds__(256) output_delta_rows(AttnParams p) {
     constexpr int kLanes = D / 8, kRows = 256 / kLanes;
@@ -166,7 +167,7 @@ __global__ void __launch_bounds__(256) output_delta_rows(AttnParams p) {
     const int64_t row_id = (int64_t)blockIdx.x * kRows + threadIdx.x / kLanes;
     const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
     float sum = 0.f;
-    if (row_id < rows) {
+    if (row_id < rows && sub * 8 < p.D) {
         const int r = (int)(row_id % p.Sq);
         const int h = (int)((row_id / p.Sq) % p.Hq);
         const int b = (int)(row_id / ((int64_t)p.Sq * p.Hq));
@@ -222,7 +223,7 @@ cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
 
 bool pipeline_backward_supported(const AttnParams& p, bool bf16) {
     (void)bf16;
-    if (p.D != 64 && p.D != 128) return false;
+    if (p.D < 8 || p.D > 128 || p.D % 8 != 0) return false;  // run as 64 or 128 channels, zero-filled by the loads
     if (p.nd != 0 || p.scale == 0.f) return false;
     if (p.Sk < 2) return false;  // a single key has P = 1: the general kernels keep dS exactly zero there
     if (!tma_compatible(p.q, p.qs, p.B, p.Hq, p.Sq) || !tma_compatible(p.k, p.ks, p.B, p.Hkv, p.Sk) ||
@@ -235,7 +236,7 @@ bool pipeline_backward_supported(const AttnParams& p, bool bf16) {
 
 // which: 0 = query-gradient kernel, 1 = key/value-gradient kernel
 cudaError_t launch_pipeline_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st) {
-    if (p.D == 128) {
+    if (p.D > 64) {
         if (which == 0) return bf16 ? launch_t<128, true, false>(p, st) : launch_t<128, false, false>(p, st);
         return bf16 ? launch_t<128, true, true>(p, st) : launch_t<128, false, true>(p, st);
     }
@@ -246,7 +247,7 @@ cudaError_t launch_pipeline_backward(const AttnParams& p, bool bf16, int which, 
 // delta for the pipeline family (rows are 16-byte aligned and channel-contiguous there)
 cudaError_t launch_pipeline_delta(const AttnParams& p, bool bf16, cudaStream_t st) {
     const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
-    if (p.D == 128) {
+    if (p.D > 64) {
         const unsigned grid = (unsigned)((rows + 15) / 16);
         if (bf16) output_delta_rows<__nv_bfloat16, 128><<<grid, 256, 0, st>>>(p);
         else output_delta_rows<__half, 128><<<grid, 256, 0, st>>>(p);

@@ -145,7 +145,7 @@ __device__ __forceinline__ void consumer_role(const Maps& maps, const AttnParams
     if (unit == 0) {
         // no visible work for this key tile: the gradients are exactly zero
         if (ok && out1)
-            for (int d = 0; d < kHalf; d += 8) {
+            for (int d = 0; d < kHalf && ch0 + d < p.D; d += 8) {
                 *reinterpret_cast<uint4*>(out1 + d) = make_uint4(0, 0, 0, 0);
                 *reinterpret_cast<uint4*>(out2 + d) = make_uint4(0, 0, 0, 0);
             }

@@ -144,7 +144,7 @@ __device__ __forceinline__ void consumer_role(const Maps& maps, const AttnParams
     if (unit == 0) {
         // no visible work for this query tile: the gradient is exactly zero
         if (ok && out)
-            for (int d = 0; d < kHalf; d += 8) *reinterpret_cast<uint4*>(out + d) = make_uint4(0, 0, 0, 0);
+            for (int d = 0; d < kHalf && ch0 + d < p.D; d += 8) *reinterpret_cast<uint4*>(out + d) = make_uint4(0, 0, 0, 0);
         return;
     }
     if (ok) ok = mbar_wait(&sh.final_done, 0, abort_word, 150);

@@ -1,5 +1,7 @@
 // Attention forward on the Blackwell tensor-memory pipeline (tcgen05 + TMEM + TMA),
-// head dim 64 or 128, FP16/BF16, causal and/or key-padding masks, grouped-query heads.
+// head dims that are multiples of 8 up to 128 (run as 64 or 128 channels: the tiled loads fill the channels
+// beyond the head with zeros, which add nothing to either product, and the tiled store drops them again),
+// FP16/BF16, causal and/or boolean masks, grouped-query heads.
 //
 // One CTA owns 256 query rows of one (batch, query head) as two 128-row tiles and walks
 // the 128-key tiles they can see.  Warp roles (320 threads):
@@ -404,9 +406,11 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
             using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
             T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] + (int64_t)row * p.os[2];
             const int64_t si = ((int64_t)b * p.Hq + h) * p.Sq + row;
-            for (int d = 0; d < D; d += 8) *reinterpret_cast<uint4*>(orow + d) = make_uint4(0, 0, 0, 0);
-            p.maximum[si] = -INFINITY;
-            p.logsum[si] = 0.f;
+            for (int d = 0; d < p.D; d += 8) *reinterpret_cast<uint4*>(orow + d) = make_uint4(0, 0, 0, 0);
+            if (p.maximum) {  // no statistics are kept for a forward pass without gradients
+                p.maximum[si] = -INFINITY;
+                p.logsum[si] = 0.f;
+            }
         }
         if (iter > 0) {
             if (ok) ok = mbar_wait(&sh.s_ready[t], iter & 1, abort_word, 32 + t);
@@ -441,7 +445,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                     tma_store_commit();
                     tma_store_wait_read();
                 }
-                if (row < p.Sq) {
+                if (row < p.Sq && p.maximum) {
                     const int64_t si = ((int64_t)b * p.Hq + h) * p.Sq + row;
                     p.maximum[si] = m_true;
                     p.logsum[si] = l > 0.f ? log2f(l) + (m_used - m_true) * c2 : 0.f;
@@ -467,7 +471,7 @@ cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
     auto kernel = p.has_mask ? pipeline_forward<D, BF16, true> : pipeline_forward<D, BF16, false>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
-    constexpr int variant = (D == 128 ? 0 : 2) + (BF16 ? 0 : 1);
+    constexpr int variant = (D == 128 ? 0 : 2) + (BF16 ? 0 : 1);  // D = channels the kernel runs with (p.D rounded up)
     const int bit = 1 << variant;
     if (!(g_configured.load() & bit)) g_configured |= bit;
     FwdMaps maps;
@@ -485,7 +489,7 @@ cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
 
 bool pipeline_forward_supported(const AttnParams& p, bool bf16) {
     (void)bf16;
-    if (p.D != 64 && p.D != 128) return false;
+    if (p.D < 8 || p.D > 128 || p.D % 8 != 0) return false;  // rows of whole 16-byte pieces
     if (p.nd != 0) return false;
     if (p.scale == 0.f || p.Sk < 2) return false;  // hidden scores are -inf; -inf * 0 is not representable in the fast path
     if (p.has_mask && (p.Sk + kTileK - 1) / kTileK > kMaxKeyTiles) return false;
@@ -497,7 +501,7 @@ bool pipeline_forward_supported(const AttnParams& p, bool bf16) {
 }
 
 cudaError_t launch_pipeline_forward(const AttnParams& p, bool bf16, cudaStream_t st) {
-    if (p.D == 128) return bf16 ? launch_t<128, true>(p, st) : launch_t<128, false>(p, st);
+    if (p.D > 64) return bf16 ? launch_t<128, true>(p, st) : launch_t<128, false>(p, st);
     return bf16 ? launch_t<64, true>(p, st) : launch_t<64, false>(p, st);
 }
 

@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
         if (ok && iter == 0 && row < p.Sq) {
             // every key tile of this row is hidden: zero output, empty statistics
             for (int d = 0; d < width; d += 8) *reinterpret_cast<uint4*>(orow + d) = make_uint4(0, 0, 0, 0);
-            if (half == 0) {
+            if (half == 0 && p.maximum) {
                 p.maximum[si] = -INFINITY;
                 p.logsum[si] = 0.f;
             }
@@ -347,7 +347,7 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
                         }
                     }
                 }
-                if (row < p.Sq && half == 0) {
+                if (row < p.Sq && half == 0 && p.maximum) {
                     p.maximum[si] = m_true;
                     p.logsum[si] = l > 0.f ? log2f(l) + (m_used - m_true) * c2 : 0.f;
                 }

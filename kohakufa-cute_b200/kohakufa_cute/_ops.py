@@ -105,12 +105,21 @@ def _center_backward(ctx, grad):
 center_keys_op.register_autograd(_center_backward, setup_context=lambda ctx, inputs, output: None)
 
 
+def _eager_forward(q, k, v, mask, scale, causal, statistics):
+    """Forward through the C ABI: split over the keys when a short query sequence would otherwise leave most
+    of the GPU idle, one launch otherwise."""
+    splits = native.split_plan(q, k, causal)
+    if splits:
+        return native.forward_split(q, k, v, mask, scale, splits, statistics)
+    return native.forward(q, k, v, mask, scale, causal, statistics)
+
+
 class _EagerAttention(torch.autograd.Function):
     """Eager route: same saved-tensor set as the custom operators, without dispatcher overhead."""
 
     @staticmethod
     def forward(ctx, q, k, v, mask, scale, causal):
-        out, maximum, logsum, blocks = native.forward(q, k, v, mask, scale, causal)
+        out, maximum, logsum, blocks = _eager_forward(q, k, v, mask, scale, causal, True)
         ctx.scale, ctx.causal, ctx.has_mask = scale, causal, mask is not None
         ctx.save_for_backward(q, k, v, maximum, logsum, blocks, out, *(() if mask is None else (mask,)))
         return out
@@ -146,4 +155,7 @@ def attention(q, k, v, *, mask=None, causal=False, scale=None):
     scale = q.shape[-1] ** -0.5 if scale is None else float(scale)
     if torch.compiler.is_compiling():
         return forward(q, k, v, mask, scale, bool(causal))[0]
+    if not (torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)):
+        # nobody will differentiate this call: no row statistics, nothing saved
+        return _eager_forward(q, k, v, mask, scale, bool(causal), False)[0]
     return _EagerAttention.apply(q, k, v, mask, scale, bool(causal))

@@ -62,6 +62,7 @@ SIGNATURES = {
     "kfa_neighborhood_backward": (ctypes.c_int, [_TP] * 10 + [ctypes.c_void_p, ctypes.c_size_t, _I64P, ctypes.c_int,
                                                               _I64P, ctypes.c_float, ctypes.c_void_p]),
     "kfa_merge_partial": (ctypes.c_int, [_TP] * 6 + [ctypes.c_float, ctypes.c_void_p]),
+    "kfa_merge_splits": (ctypes.c_int, [_TP] * 6 + [ctypes.c_float, ctypes.c_void_p]),
     "kfa_cache_size": (ctypes.c_int, []),
     "kfa_clear_cache": (None, []),
     "kfa_launch_count": (ctypes.c_uint64, []),
@@ -163,20 +164,98 @@ def _blocks_shape(q, k, mask):
     )
 
 
-def forward(q, k, v, mask, scale, causal):
-    """(out, maximum, logsum, blocks) - mirrors the reference extension's ``forward`` (native.cpp:1034)."""
+def forward(q, k, v, mask, scale, causal, statistics=True):
+    """(out, maximum, logsum, blocks) - mirrors the reference extension's ``forward`` (native.cpp:1034).
+    With ``statistics=False`` (a forward pass nobody will differentiate) the two row statistics are neither
+    allocated nor written and come back as ``None``."""
     lib = library()
     q, k, v = _plain(q), _plain(k), _plain(v)
     with torch.cuda.device(q.device):
         out = torch.empty_like(q)
-        maximum = torch.empty(q.shape[:-1], device=q.device, dtype=torch.float32)
-        logsum = torch.empty_like(maximum)
+        maximum = torch.empty(q.shape[:-1], device=q.device, dtype=torch.float32) if statistics else None
+        logsum = torch.empty_like(maximum) if statistics else None
         if mask is None:
             blocks = torch.empty((1, 1, 1, 1), device=q.device, dtype=torch.int32)
         else:
             blocks = torch.empty(_blocks_shape(q, k, mask), device=q.device, dtype=torch.int32)
         records = [describe(t) for t in (q, k, v, mask, out, maximum, logsum, blocks if mask is not None else None)]
         _check(lib.kfa_forward(*[_ref(r) for r in records], float(scale), int(bool(causal)), _stream(q.device)))
+    return out, maximum, logsum, blocks
+
+
+def split_plan(q, k, causal):
+    """Number of key ranges to split a forward call into, or 0.  A short query sequence against a long key
+    sequence gives the forward kernel one CTA per (batch, head) and leaves most of the GPU idle; splitting the
+    keys over CTAs and merging the partial results fills it (the reference's split forward,
+    split_forward.py:125-245, serves the same shapes)."""
+    B, Hq, Sq, D = q.shape
+    Sk = k.shape[2]
+    if causal or Sq > 256 or Sk < 4096 or D > 128 or D % 8:
+        return 0
+    ctas = B * Hq
+    if 2 * ctas > 148:
+        return 0
+    splits = min(148 // ctas, Sk // 1024, 32)
+    return splits if splits >= 2 else 0
+
+
+def forward_split(q, k, v, mask, scale, splits, statistics=True):
+    """Forward pass split over the key axis (non-causal): ``kfa_forward`` on ``splits`` key ranges, folded into
+    the batch axis of one launch per batch element (a remainder range gets its own), then ``kfa_merge_splits``.
+    The partial outputs are normalised per range and rounded to the 16-bit type before the merge, which rounds
+    the result once more.  Returns ``(out, maximum, logsum, blocks)`` like ``forward``; the statistics cover the
+    whole key range, so the ordinary backward applies."""
+    lib = library()
+    q, k, v = _plain(q), _plain(k), _plain(v)
+    B, Hq, Sq, D = q.shape
+    Hkv, Sk = k.shape[1], k.shape[2]
+    chunk = -(-Sk // splits)
+    chunk = -(-chunk // 128) * 128
+    full, tail = Sk // chunk, Sk % chunk
+    parts = full + (1 if tail else 0)
+    with torch.cuda.device(q.device):
+        stream = _stream(q.device)
+        out = torch.empty_like(q)
+        maximum = torch.empty(q.shape[:-1], device=q.device, dtype=torch.float32) if statistics else None
+        logsum = torch.empty_like(maximum) if statistics else None
+        part_out = torch.empty((B, parts, Hq, Sq, D), device=q.device, dtype=q.dtype)
+        part_max = torch.empty((B, parts, Hq, Sq), device=q.device, dtype=torch.float32)
+        part_log = torch.empty_like(part_max)
+
+        def ranges(t, b, first, count, length):
+            """[count, heads, length, D] view of batch element b: range i starts at key first + i * length."""
+            return torch.as_strided(t, (count, t.shape[1], length, t.shape[3]),
+                                    (length * t.stride(2), t.stride(1), t.stride(2), t.stride(3)),
+                                    t.storage_offset() + b * t.stride(0) + first * t.stride(2))
+
+        def masks(b, first, count, length):
+            if mask is None:
+                return None
+            return torch.as_strided(mask, (count, Hq, Sq, length),
+                                    (length * mask.stride(3), mask.stride(1), mask.stride(2), mask.stride(3)),
+                                    mask.storage_offset() + b * mask.stride(0) + first * mask.stride(3))
+
+        for b in range(B):
+            pieces = [(0, full, chunk)] if full else []
+            if tail:
+                pieces.append((full * chunk, 1, tail))
+            done = 0
+            for first, count, length in pieces:
+                qs = q[b:b + 1].expand(count, Hq, Sq, D).contiguous()
+                ks, vs, ms = ranges(k, b, first, count, length), ranges(v, b, first, count, length), masks(b, first, count, length)
+                blocks = None if ms is None else torch.empty(_blocks_shape(qs, ks, ms), device=q.device, dtype=torch.int32)
+                records = [describe(t) for t in (qs, ks, vs, ms, part_out[b, done:done + count], part_max[b, done:done + count],
+                                                 part_log[b, done:done + count], blocks)]
+                _check(lib.kfa_forward(*[_ref(r) for r in records], float(scale), 0, stream))
+                done += count
+            records = [describe(t) for t in (out[b:b + 1], None if maximum is None else maximum[b:b + 1],
+                                             None if logsum is None else logsum[b:b + 1], part_out[b].unsqueeze(1),
+                                             part_max[b].unsqueeze(1), part_log[b].unsqueeze(1))]
+            _check(lib.kfa_merge_splits(*[_ref(r) for r in records], float(scale), stream))
+        if mask is None:
+            blocks = torch.empty((1, 1, 1, 1), device=q.device, dtype=torch.int32)
+        else:
+            blocks = pack_mask(q, k, mask) if statistics else torch.empty((1, 1, 1, 1), device=q.device, dtype=torch.int32)
     return out, maximum, logsum, blocks
 
 

@@ -163,6 +163,42 @@ def test_general_head_dims(shape, dtype):
     check_against_oracle(actual, q, k, v, dout, None, causal, None)
 
 
+PADDED_HEAD_SHAPES = [
+    # B, Hq, Hkv, Sq, Sk, D, causal: head dims that are multiples of 8 run on the tensor-memory pipeline as 64 or
+    # 128 channels (the loads zero-fill the rest, the stores drop it)
+    (1, 4, 2, 300, 300, 80, True),
+    (2, 2, 2, 129, 257, 96, False),
+    (1, 2, 1, 513, 140, 8, True),
+    (1, 4, 1, 640, 640, 120, True),
+    (1, 2, 2, 70, 330, 40, False),
+    (1, 2, 1, 260, 260, 72, True),
+]
+
+
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
+@pytest.mark.parametrize("shape", PADDED_HEAD_SHAPES)
+def test_head_dims_padded_by_the_tiled_loads(shape, dtype):
+    B, Hq, Hkv, Sq, Sk, D, causal = shape
+    q, k, v, dout = make_inputs(B, Hq, Hkv, Sq, Sk, D, dtype, seed=D + Sq)
+    assert native().selected_family(q, k, v, None, causal) == 1
+    assert native().selected_family(q, k, v, None, causal, backward=True) == 1
+    # poison behind every row end would show a store or load that runs past the head's channels
+    wide = [torch.full((*t.shape[:-1], t.shape[-1] + 8), float("nan"), device=t.device, dtype=t.dtype) for t in (q, k, v)]
+    for big, t in zip(wide, (q, k, v)):
+        big[..., :D] = t
+    views = [big[..., :D] for big in wide]
+    assert native().selected_family(*views, None, causal, backward=True) == 1
+    actual = run_attention(api().attention, *views, dout, causal=causal)
+    check_against_oracle(actual, q, k, v, dout, None, causal, None)
+    plain = run_attention(api().attention, q, k, v, dout, causal=causal)
+    for a, b in zip(actual, plain):
+        assert torch.equal(a, b)
+    # a key-padding mask together with the padded channels
+    mask = (torch.arange(Sk, device="cuda") < Sk - 37)[None, None, None, :]
+    masked = run_attention(api().attention, q, k, v, dout, mask=mask, causal=causal)
+    check_against_oracle(masked, q, k, v, dout, mask, causal, None)
+
+
 @pytest.mark.parametrize("scale", (0.0, -0.125, 0.3))
 @pytest.mark.parametrize("D", (64, 96))
 def test_signed_and_zero_scale(scale, D):
