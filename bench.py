@@ -546,6 +546,36 @@ def sdpa_comparator(device, steps=20):
         return {"what": "torch SDPA, cuDNN backend, d128_4k fwd+bwd", "unavailable": f"{type(error).__name__}: {error}"[:200]}
 
 
+def decode_probe(device, steps=200):
+    """One query row per head against 32768 keys (B=1, Hq=32, Hkv=8, D=128, bf16), forward only and without
+    gradients: the split-over-keys forward.  Memory-bound: reported as time and as K/V bytes per second."""
+    import kohakufa_cute
+
+    try:
+        gen = torch.Generator(device=device).manual_seed(9)
+        sets = []
+        for _ in range(4):  # rotate over K/V sets that together exceed L2
+            q = torch.randn(1, 32, 1, 128, device=device, dtype=torch.bfloat16, generator=gen)
+            k, v = (torch.randn(1, 8, 32768, 128, device=device, dtype=torch.bfloat16, generator=gen) for _ in range(2))
+            sets.append((q, k, v))
+        with torch.no_grad():
+            for q, k, v in sets:
+                kohakufa_cute.attention(q, k, v)
+            torch.cuda.synchronize()
+            b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            b.record()
+            for i in range(steps):
+                kohakufa_cute.attention(*sets[i % 4])
+            e.record()
+            torch.cuda.synchronize()
+        ms = b.elapsed_time(e) / steps
+        kv_bytes = 2 * 8 * 32768 * 128 * 2
+        return {"workload": "decode (B1 Hq32 Hkv8 Sq1 Sk32768 D128, forward only, no gradients, eager)",
+                "ms_per_call": ms, "kv_gbs": kv_bytes / (ms * 1e-3) / 1e9}
+    except Exception as error:
+        return {"workload": "decode", "error": f"{type(error).__name__}: {error}"[:200]}
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -610,6 +640,8 @@ def main():
             torch.cuda.empty_cache()
         status = status or native.device_status(reset=True)
     comparator = sdpa_comparator(device) if (rank == 0 and not args.no_others and world == 1) else None
+    if rank == 0 and not args.no_others and world == 1 and args.workload == "llm_gqa":
+        others.append(decode_probe(device))
 
     flops = algorithmic_flops(w)
     jobs = 1 if w.get("ring") else world
