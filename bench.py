@@ -56,6 +56,10 @@ WORKLOADS = {
                      masked_fraction=0.1, ring=True),
     "dit_ring_small": dict(B=1, Hq=24, Hkv=24, S=65536, D=128, dtype="bf16", causal=False, center_keys=False, seed=6,
                            masked_fraction=0.1, ring=True),
+    # A causal language-model sequence of 131072 tokens over the ranks: zig-zag shards (rank r owns chunks r and
+    # 2N-1-r of 2N), so every rank has the same visible work in every ring step.  Random data: a shard is a shard.
+    "llm_ring_causal": dict(B=1, Hq=32, Hkv=8, S=131072, D=128, dtype="bf16", causal=True, center_keys=False, seed=8,
+                            ring=True),
     # the reference's published 2-D neighbourhood shape on B200: 151.28 us forward+backward (CUDA-graph median)
     "neighborhood_2d": dict(B=1, Hq=8, Hkv=8, S=64 * 64, D=64, dtype="bf16", causal=False, center_keys=False,
                             seed=7, grid=(64, 64), window=(7, 7), graph=True,
@@ -66,7 +70,7 @@ WORKLOADS = {
 # short runs added to the headline line: (workload, steps, minimum seconds of timed region)
 OTHERS_SINGLE = (("wide_head", 20, 0.2), ("d128_4k", 20, 0.2), ("dit_masked", 3, 0.3), ("neighborhood_3d", 20, 0.2),
                  ("neighborhood_2d", 20, 0.2))
-OTHERS_MULTI = (("dit_ring", 2, 0.0),)
+OTHERS_MULTI = (("dit_ring", 2, 0.0), ("llm_ring_causal", 2, 0.0))
 
 # GEMMs of the seven algorithmic ones (S, PV forward; S, dP, dV, dK, dQ backward counted as 5) attributed to a
 # kernel, and GEMMs it executes.  The two backward owners each recompute S and dP: 9 executed per 7.
@@ -139,8 +143,10 @@ def build_step(w):
     if w.get("ring"):
         from kohakufa_cute import parallel
 
+        causal = bool(w["causal"])
+
         def forward(q, k, v, mask):
-            return parallel.ring_attention(q, k, v, key_mask=mask)
+            return parallel.ring_attention(q, k, v, key_mask=mask, causal=causal)
     elif "window" in w:
         grid, window = w["grid"], w["window"]
 
@@ -162,7 +168,8 @@ def describe_config(w, world, launch, l2_note):
     """The ``config`` object; both arms print the same keys for the same workload."""
     return {"workload": w["name"], "launch": launch, "B": w["B"], "Hq": w["Hq"], "Hkv": w["Hkv"], "S": w["S"],
             "D": w["D"], "causal": w["causal"], "center_keys": w["center_keys"],
-            "sharding": (f"ring context parallel, S/{world} per rank" if w.get("ring") else f"replica-per-gpu x{world}"),
+            "sharding": ((f"ring context parallel, S/{world} per rank" + (", zig-zag chunks" if w["causal"] else ""))
+                         if w.get("ring") else f"replica-per-gpu x{world}"),
             "l2": l2_note,
             "input_stds": {"q": 8.0, "k_offset": 2.0, "dout": math.sqrt(1e-3)} if w["name"].startswith("llm_gqa") else None}
 

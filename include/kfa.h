@@ -172,6 +172,37 @@ KFA_API int kfa_merge_partial(kfa_tensor* acc_out, kfa_tensor* acc_maximum, kfa_
                       const kfa_tensor* part_logsum, float scale, void* stream);
 
 /*
+ * Block-wise forms for callers that hold only one block of a longer sequence at a time (ring context
+ * parallelism; no counterpart in the reference, whose split forward keeps FP32 partial outputs with (maximum, sum)
+ * pairs and merges them afterwards: split_forward.py:125-245).  Nothing is rounded to the 16-bit type between
+ * blocks.  Served by the tensor-memory pipeline family only (head dims that are multiples of 8 up to 128, 16-byte
+ * addressable rows, non-zero scale, at least two keys); other operands return KFA_INVALID_ARGUMENT.
+ *
+ * kfa_forward_running attends q to one block (k, v, mask) and folds the result into a running state with the
+ * (maximum, sum) merge of split_forward.py:219-245, inside the kernel's epilogue:
+ *   acc [B,Hq,Sq,D] f32, unit channel stride: unnormalised output relative to run_maximum (start: zeros)
+ *   run_maximum [B,Hq,Sq] f32, unit row stride: unscaled row maximum so far (start: -inf)
+ *   run_sum     [B,Hq,Sq] f32, same strides: sum of 2^((s - run_maximum) |scale| log2e) so far (start: zeros)
+ * kfa_finish_running divides once, rounds `out` once and writes the statistics of kfa_forward's contract
+ * (maximum = run_maximum, logsum = log2(run_sum); rows that saw no key: zeros, -inf, 0).  `maximum` may be the
+ * same tensor as `run_maximum`, `logsum` the same as `run_sum`.
+ *
+ * kfa_backward_partial is kfa_backward for one (query block, key block) pair against the statistics of the whole
+ * sequence, with float32 gradients (unit channel stride, any other strides): dq is overwritten or, with
+ * accumulate_dq != 0, added to; dk and dv likewise with accumulate_dkv.  Workspace as for kfa_backward.
+ */
+KFA_API int kfa_forward_running(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
+                        kfa_tensor* acc, kfa_tensor* run_maximum, kfa_tensor* run_sum, kfa_tensor* blocks,
+                        float scale, int causal, void* stream);
+KFA_API int kfa_finish_running(const kfa_tensor* acc, const kfa_tensor* run_maximum, const kfa_tensor* run_sum,
+                       kfa_tensor* out, kfa_tensor* maximum, kfa_tensor* logsum, void* stream);
+KFA_API int kfa_backward_partial(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
+                         const kfa_tensor* out, const kfa_tensor* maximum, const kfa_tensor* logsum,
+                         const kfa_tensor* dout, const kfa_tensor* blocks, kfa_tensor* dq, kfa_tensor* dk,
+                         kfa_tensor* dv, void* workspace, size_t workspace_bytes, float scale, int causal,
+                         int accumulate_dq, int accumulate_dkv, void* stream);
+
+/*
  * Merge step of a forward pass split over the key axis (short query sequences against long key
  * sequences, where one CTA per head would leave the GPU idle): the caller runs kfa_forward on `splits`
  * key ranges and this call folds the partial results, with the arithmetic of the reference's split

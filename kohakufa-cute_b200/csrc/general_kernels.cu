@@ -548,6 +548,28 @@ __global__ void __launch_bounds__(128) merge_partial(float* acc, float* am, floa
     }
 }
 
+// Closes a running forward state (block-wise calls over a longer key sequence): one division per row, the output
+// rounded once to the 16-bit type, and the statistics of the operator's contract (unscaled maximum, log2 of the sum).
+template <typename T>
+__global__ void __launch_bounds__(128) finish_running(T* out, float* maximum, float* logsum, const float* acc,
+                                                      const float* run_max, const float* run_sum, int64_t rows, int D,
+                                                      int64_t a_b, int64_t a_h, int64_t a_s, int64_t o_b, int64_t o_h,
+                                                      int64_t o_s, int64_t o_d, int H, int S) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int s = (int)(row % S), h = (int)((row / S) % H), b = (int)(row / ((int64_t)S * H));
+    const float l = run_sum[row];
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const float* arow = acc + (int64_t)b * a_b + (int64_t)h * a_h + (int64_t)s * a_s;
+    T* orow = out + (int64_t)b * o_b + (int64_t)h * o_h + (int64_t)s * o_s;
+    for (int d = lane; d < D; d += 32) orow[(int64_t)d * o_d] = from_float<T>(arow[d] * inv);
+    if (lane == 0) {
+        maximum[row] = l > 0.f ? run_max[row] : -INFINITY;
+        logsum[row] = l > 0.f ? log2f(l) : 0.f;
+    }
+}
+
 // Merges the partial results of a forward pass split over the key axis: `splits` normalised outputs with their
 // (maximum, logsum) pairs -> one output row, rounded once, and the statistics of the whole key range.
 // part is [splits, rows, D] (16-bit, contiguous), pm / pl are [splits, rows].
@@ -725,6 +747,21 @@ cudaError_t launch_merge_partial(float* acc, float* am, float* al, const void* p
         merge_partial<__half><<<(unsigned)blocks_for(rows, 4), 128, 0, st>>>(acc, am, al, (const __half*)part, pm, pl,
                                                                             rows, D, c2, D, ps[0], ps[1], ps[2],
                                                                             ps[3], H, S);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_finish_running(void* out, float* maximum, float* logsum, const float* acc, const float* run_max,
+                                  const float* run_sum, bool bf16, int B, int H, int S, int D, const int64_t* as,
+                                  const int64_t* os, cudaStream_t st) {
+    const int64_t rows = (int64_t)B * H * S;
+    if (bf16)
+        finish_running<__nv_bfloat16><<<(unsigned)blocks_for(rows, 4), 128, 0, st>>>(
+            (__nv_bfloat16*)out, maximum, logsum, acc, run_max, run_sum, rows, D, as[0], as[1], as[2], os[0], os[1],
+            os[2], os[3], H, S);
+    else
+        finish_running<__half><<<(unsigned)blocks_for(rows, 4), 128, 0, st>>>((__half*)out, maximum, logsum, acc,
+                                                                              run_max, run_sum, rows, D, as[0], as[1],
+                                                                              as[2], os[0], os[1], os[2], os[3], H, S);
     return cudaGetLastError();
 }
 

@@ -629,19 +629,39 @@ size_t kfa_backward_workspace_bytes(const kfa_tensor* q, const kfa_tensor* k) {
     return delta_bytes(q) + wide_extra_bytes(q, k);
 }
 
-int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
-                 const kfa_tensor* out, const kfa_tensor* maximum, const kfa_tensor* logsum, const kfa_tensor* dout,
-                 const kfa_tensor* blocks, kfa_tensor* dq, kfa_tensor* dk, kfa_tensor* dv, void* workspace,
-                 size_t workspace_bytes, float scale, int causal, void* stream) {
+}  // extern "C"
+
+namespace {
+
+// FP32 gradient tensor of a block-wise call: the shape of `like`, float32, channel-contiguous.
+int check_f32_like(const kfa_tensor* t, const kfa_tensor* like, const char* name) {
+    if (!t || !t->data || t->dtype != KFA_F32 || !same_shape(t, like) || t->strides[3] != 1)
+        return fail(KFA_INVALID_ARGUMENT, "%s must be a float32 tensor with the shape of its source and unit channel stride", name);
+    return 0;
+}
+
+// grad_f32 = 0: the operator's backward.  Otherwise the block-wise form: FP32 gradients (bit 0), added to dq
+// (bit 1) and to dk, dv (bit 2) instead of overwriting them.
+int backward_impl(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
+                  const kfa_tensor* out, const kfa_tensor* maximum, const kfa_tensor* logsum, const kfa_tensor* dout,
+                  const kfa_tensor* blocks, kfa_tensor* dq, kfa_tensor* dk, kfa_tensor* dv, void* workspace,
+                  size_t workspace_bytes, float scale, int causal, int grad_f32, void* stream) {
     if (int e = check_device_ok()) return e;
     if (int e = check_qkv(q, k, v)) return e;
     kfa::AttnParams p;
     if (int e = fill_common(p, q, k, v, mask, scale, causal, static_cast<cudaStream_t>(stream))) return e;
     if (int e = check_like(out, q, "out")) return e;
     if (int e = check_like(dout, q, "dout")) return e;
-    if (int e = check_like(dq, q, "dq")) return e;
-    if (int e = check_like(dk, k, "dk")) return e;
-    if (int e = check_like(dv, v, "dv")) return e;
+    if (grad_f32) {
+        if (int e = check_f32_like(dq, q, "dq")) return e;
+        if (int e = check_f32_like(dk, k, "dk")) return e;
+        if (int e = check_f32_like(dv, v, "dv")) return e;
+    } else {
+        if (int e = check_like(dq, q, "dq")) return e;
+        if (int e = check_like(dk, k, "dk")) return e;
+        if (int e = check_like(dv, v, "dv")) return e;
+    }
+    p.grad_f32 = grad_f32;
     if (!contiguous3(maximum, p.B, p.Hq, p.Sq) || !contiguous3(logsum, p.B, p.Hq, p.Sq))
         return fail(KFA_INVALID_ARGUMENT, "maximum/logsum must be contiguous float32 [B,Hq,Sq]");
     if (int e = bind_blocks(p, blocks)) return e;
@@ -664,6 +684,10 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool bf16 = q->dtype == KFA_BF16;
     const bool pipeline = kfa::pipeline_backward_supported(p, bf16);
+    if (grad_f32 && !pipeline)
+        return fail(KFA_INVALID_ARGUMENT,
+                    "block-wise backward needs the tensor-memory pipeline family: head dims that are multiples of 8 "
+                    "up to 128, 16-byte addressable rows, a non-zero scale and at least two keys");
     const bool wide = !pipeline && kfa::wide_backward_supported(p) && wide_extra_bytes(q, k) > 0;
     // Wide heads: the first score kernel (P_low) needs only the forward's statistics, so delta runs on a side
     // stream beside it and joins before the second score kernel.  (Serial while per-kernel timing is on.)
@@ -738,6 +762,91 @@ int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, 
         ce = timed("general_backward_kv", st, [&] { return kfa::launch_general_backward(p, bf16, 1, st); });
         if (ce != cudaSuccess) return cuda_fail(ce, "general backward (dK/dV) launch");
     }
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int kfa_backward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
+                 const kfa_tensor* out, const kfa_tensor* maximum, const kfa_tensor* logsum, const kfa_tensor* dout,
+                 const kfa_tensor* blocks, kfa_tensor* dq, kfa_tensor* dk, kfa_tensor* dv, void* workspace,
+                 size_t workspace_bytes, float scale, int causal, void* stream) {
+    return backward_impl(q, k, v, mask, out, maximum, logsum, dout, blocks, dq, dk, dv, workspace, workspace_bytes,
+                         scale, causal, 0, stream);
+}
+
+int kfa_backward_partial(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
+                         const kfa_tensor* out, const kfa_tensor* maximum, const kfa_tensor* logsum,
+                         const kfa_tensor* dout, const kfa_tensor* blocks, kfa_tensor* dq, kfa_tensor* dk,
+                         kfa_tensor* dv, void* workspace, size_t workspace_bytes, float scale, int causal,
+                         int accumulate_dq, int accumulate_dkv, void* stream) {
+    return backward_impl(q, k, v, mask, out, maximum, logsum, dout, blocks, dq, dk, dv, workspace, workspace_bytes,
+                         scale, causal, 1 | (accumulate_dq ? 2 : 0) | (accumulate_dkv ? 4 : 0), stream);
+}
+
+int kfa_forward_running(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, const kfa_tensor* mask,
+                        kfa_tensor* acc, kfa_tensor* run_maximum, kfa_tensor* run_sum, kfa_tensor* blocks,
+                        float scale, int causal, void* stream) {
+    if (int e = check_device_ok()) return e;
+    if (int e = check_qkv(q, k, v)) return e;
+    kfa::AttnParams p;
+    if (int e = fill_common(p, q, k, v, mask, scale, causal, static_cast<cudaStream_t>(stream))) return e;
+    if (int e = check_f32_like(acc, q, "acc")) return e;
+    auto rows3 = [&](const kfa_tensor* t) {
+        return t && t->data && t->dtype == KFA_F32 && t->ndim == 3 && t->sizes[0] == p.B && t->sizes[1] == p.Hq &&
+               t->sizes[2] == p.Sq && t->strides[2] == 1;
+    };
+    if (!rows3(run_maximum) || !rows3(run_sum) || run_maximum->strides[0] != run_sum->strides[0] ||
+        run_maximum->strides[1] != run_sum->strides[1])
+        return fail(KFA_INVALID_ARGUMENT,
+                    "running maximum/sum must be float32 [B,Hq,Sq] with unit row stride and equal strides");
+    p.ss[0] = run_maximum->strides[0];
+    p.ss[1] = run_maximum->strides[1];
+    if (int e = bind_blocks(p, blocks)) return e;
+    p.out = acc->data;
+    copy4(p.os, acc->strides);
+    p.maximum = static_cast<float*>(run_maximum->data);
+    p.run_sum = static_cast<float*>(run_sum->data);
+    p.running = 1;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool bf16 = q->dtype == KFA_BF16;
+    if (!kfa::pipeline_forward_supported(p, bf16))
+        return fail(KFA_INVALID_ARGUMENT,
+                    "block-wise forward needs the tensor-memory pipeline family: head dims that are multiples of 8 "
+                    "up to 128, 16-byte addressable rows, a non-zero scale and at least two keys");
+    cudaError_t ce;
+    if (p.has_mask) {
+        int64_t n[4];
+        block_extents(p, n);
+        ce = timed("pack_mask", st, [&] { return kfa::launch_pack_mask(p, (int)n[0], (int)n[1], (int)n[2], (int)n[3], st); });
+        if (ce != cudaSuccess) return cuda_fail(ce, "pack_mask launch");
+    }
+    ce = timed("pipeline_forward", st, [&] { return kfa::launch_pipeline_forward(p, bf16, st); });
+    if (ce != cudaSuccess) return cuda_fail(ce, "pipeline forward launch");
+    return 0;
+}
+
+int kfa_finish_running(const kfa_tensor* acc, const kfa_tensor* run_maximum, const kfa_tensor* run_sum,
+                       kfa_tensor* out, kfa_tensor* maximum, kfa_tensor* logsum, void* stream) {
+    if (!acc || !out || !acc->data || !out->data || acc->ndim != 4 || out->ndim != 4 || !same_shape(acc, out) ||
+        acc->dtype != KFA_F32 || !is_half_type(out) || acc->strides[3] != 1)
+        return fail(KFA_INVALID_ARGUMENT, "finish requires a float32 accumulator and an FP16/BF16 output of one 4D shape");
+    const int64_t B = acc->sizes[0], H = acc->sizes[1], S = acc->sizes[2], D = acc->sizes[3];
+    if (B * H * S > INT32_MAX * int64_t(4)) return fail(KFA_TOO_LARGE, "finish: too many rows");
+    if (!contiguous3(run_maximum, B, H, S) || !contiguous3(run_sum, B, H, S) || !contiguous3(maximum, B, H, S) ||
+        !contiguous3(logsum, B, H, S))
+        return fail(KFA_INVALID_ARGUMENT, "finish statistics must be contiguous float32 [B,H,S]");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t ce = timed("finish_running", st, [&] {
+        return kfa::launch_finish_running(out->data, static_cast<float*>(maximum->data),
+                                          static_cast<float*>(logsum->data), static_cast<const float*>(acc->data),
+                                          static_cast<const float*>(run_maximum->data),
+                                          static_cast<const float*>(run_sum->data), out->dtype == KFA_BF16, (int)B,
+                                          (int)H, (int)S, (int)D, acc->strides, out->strides, st);
+    });
+    if (ce != cudaSuccess) return cuda_fail(ce, "finish launch");
     return 0;
 }
 

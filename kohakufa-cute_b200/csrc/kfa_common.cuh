@@ -44,6 +44,16 @@ struct AttnParams {
     int ext[3];
     int win[3];
     int two_term;
+    // Block-wise calls (one block of a longer key sequence, or one of its gradient contributions):
+    // running != 0: the forward folds its block into a running FP32 state instead of writing a normalised output:
+    //   `out` is the unnormalised FP32 accumulator [B,Hq,Sq,D] (strides `os`), `maximum` the running unscaled row
+    //   maximum and `run_sum` the running sum of probabilities relative to it (both [B,Hq,Sq], unit row stride,
+    //   batch and head strides `ss`).
+    // grad_f32 bit 0: dq/dk/dv are FP32 tensors; bit 1: add to dq instead of overwriting it; bit 2: same for dk, dv.
+    float* run_sum;
+    int64_t ss[2];
+    int running;
+    int grad_f32;
     int* status;      // device-visible status word (mapped host memory)
     int* abort_flag;  // device memory: set by the first CTA whose bounded wait gives up; later CTAs skip their work
 };

@@ -26,6 +26,10 @@ cudaError_t launch_merge_splits(void* out, float* maximum, float* logsum, const 
                                 const float* pl, bool bf16, int splits, int B, int H, int S, int D, const int64_t* os,
                                 float scale, cudaStream_t st);
 
+cudaError_t launch_finish_running(void* out, float* maximum, float* logsum, const float* acc, const float* run_max,
+                                  const float* run_sum, bool bf16, int B, int H, int S, int D, const int64_t* as,
+                                  const int64_t* os, cudaStream_t st);
+
 cudaError_t launch_neighborhood_forward(const AttnParams& p, bool bf16, cudaStream_t st);
 cudaError_t launch_neighborhood_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st);
 

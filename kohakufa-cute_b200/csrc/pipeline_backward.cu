@@ -205,7 +205,9 @@ cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
     if (!encode_bhsd_map(&maps.k, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kTile)) return cudaErrorInvalidValue;
     if (!encode_bhsd_map(&maps.v, p.v, dt, p.D, p.Sk, p.Hkv, p.B, p.vs, 64, kTile)) return cudaErrorInvalidValue;
     if (!encode_bhsd_map(&maps.g, p.dout, dt, p.D, p.Sq, p.Hq, p.B, p.gs, 64, kTile)) return cudaErrorInvalidValue;
-    if (KV) {
+    if (p.grad_f32) {
+        maps.dq = maps.dk = maps.dv = maps.q;  // not used: FP32 gradients are written with plain stores
+    } else if (KV) {
         if (!encode_bhsd_map(&maps.dk, p.dk, dt, p.D, p.Sk, p.Hkv, p.B, p.dks, 64, kTile)) return cudaErrorInvalidValue;
         if (!encode_bhsd_map(&maps.dv, p.dv, dt, p.D, p.Sk, p.Hkv, p.B, p.dvs, 64, kTile)) return cudaErrorInvalidValue;
         maps.dq = maps.dk;
@@ -229,9 +231,16 @@ bool pipeline_backward_supported(const AttnParams& p, bool bf16) {
     if (!tma_compatible(p.q, p.qs, p.B, p.Hq, p.Sq) || !tma_compatible(p.k, p.ks, p.B, p.Hkv, p.Sk) ||
         !tma_compatible(p.v, p.vs, p.B, p.Hkv, p.Sk) || !tma_compatible(p.dout, p.gs, p.B, p.Hq, p.Sq))
         return false;
-    // 16-byte vector stores / loads per row
+    if (!tma_compatible(p.out, p.os, p.B, p.Hq, p.Sq)) return false;  // 16-byte vector loads per row (delta)
+    if (p.grad_f32) {  // FP32 rows read and written as 16-byte vectors
+        auto rows_ok = [](const void* ptr, const int64_t* st) {
+            return st[3] == 1 && reinterpret_cast<uintptr_t>(ptr) % 16 == 0 && st[0] % 4 == 0 && st[1] % 4 == 0 &&
+                   st[2] % 4 == 0;
+        };
+        return rows_ok(p.dq, p.dqs) && rows_ok(p.dk, p.dks) && rows_ok(p.dv, p.dvs);
+    }
     return tma_compatible(p.dq, p.dqs, p.B, p.Hq, p.Sq) && tma_compatible(p.dk, p.dks, p.B, p.Hkv, p.Sk) &&
-           tma_compatible(p.dv, p.dvs, p.B, p.Hkv, p.Sk) && tma_compatible(p.out, p.os, p.B, p.Hq, p.Sq);
+           tma_compatible(p.dv, p.dvs, p.B, p.Hkv, p.Sk);
 }
 
 // which: 0 = query-gradient kernel, 1 = key/value-gradient kernel

@@ -116,5 +116,22 @@ struct Work {
     __device__ __forceinline__ int query_head(int g) const { return KV ? head * groups + g : head; }
 };
 
+// FP32 gradient rows for block-wise callers (one block of a longer sequence per call): `n` accumulator values
+// times `mul` are written to, or added to, `row[0..n)` as 16-byte vectors; channels at or beyond `valid` are skipped.
+template <int N>
+__device__ __forceinline__ void put_f32(float* row, const uint32_t (&v)[N], int valid, float mul, bool add) {
+#pragma unroll
+    for (int e = 0; e < N; e += 4) {
+        if (e < valid) {
+            float4 a = add ? *reinterpret_cast<const float4*>(row + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+            a.x += __uint_as_float(v[e]) * mul;
+            a.y += __uint_as_float(v[e + 1]) * mul;
+            a.z += __uint_as_float(v[e + 2]) * mul;
+            a.w += __uint_as_float(v[e + 3]) * mul;
+            *reinterpret_cast<float4*>(row + e) = a;
+        }
+    }
+}
+
 }  // namespace bwd
 }  // namespace kfa

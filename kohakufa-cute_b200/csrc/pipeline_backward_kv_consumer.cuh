@@ -142,6 +142,38 @@ __device__ __forceinline__ void consumer_role(const Maps& maps, const AttnParams
         out2 = reinterpret_cast<T*>(p.dv) + (int64_t)w.b * p.dvs[0] + (int64_t)w.head * p.dvs[1] +
                (int64_t)owner_row * p.dvs[2] + ch0;
     }
+    if (p.grad_f32) {
+        // FP32 partial gradients of a block-wise call: plain vector stores (or read-add-write) per row
+        const bool add = (p.grad_f32 & 4) != 0;
+        if (!ok) return;
+        const bool live = owner_row < p.Sk;  // (the tensor-memory loads below are warp-wide: every lane runs them)
+        float* f1 = reinterpret_cast<float*>(p.dk) + (int64_t)w.b * p.dks[0] + (int64_t)w.head * p.dks[1] +
+                    (int64_t)owner_row * p.dks[2] + ch0;
+        float* f2 = reinterpret_cast<float*>(p.dv) + (int64_t)w.b * p.dvs[0] + (int64_t)w.head * p.dvs[1] +
+                    (int64_t)owner_row * p.dvs[2] + ch0;
+        if (unit == 0) {
+            if (!add && live)
+                for (int d = 0; d < kHalf && ch0 + d < p.D; d += 4) {
+                    *reinterpret_cast<float4*>(f1 + d) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    *reinterpret_cast<float4*>(f2 + d) = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            return;
+        }
+        if (!mbar_wait(&sh.final_done, 0, abort_word, 150)) return;
+        tc_fence_after();
+        constexpr int kStepF = kHalf < 32 ? 16 : 32;
+#pragma unroll
+        for (int c = 0; c < kHalf; c += kStepF) {
+            uint32_t v[kStepF];
+            tmem_ld(lane_base + kColDk + ch0 + c, v);
+            tmem_wait_ld();
+            put_f32(f1 + c, v, live ? p.D - ch0 - c : 0, p.scale, add);
+            tmem_ld(lane_base + kColDv + ch0 + c, v);
+            tmem_wait_ld();
+            put_f32(f2 + c, v, live ? p.D - ch0 - c : 0, 1.f, add);
+        }
+        return;
+    }
     if (unit == 0) {
         // no visible work for this key tile: the gradients are exactly zero
         if (ok && out1)

@@ -141,6 +141,31 @@ __device__ __forceinline__ void consumer_role(const Maps& maps, const AttnParams
     if (owner_row < p.Sq)
         out = reinterpret_cast<T*>(p.dq) + (int64_t)w.b * p.dqs[0] + (int64_t)w.head * p.dqs[1] +
               (int64_t)owner_row * p.dqs[2] + ch0;
+    if (p.grad_f32) {
+        // FP32 partial gradient of a block-wise call: plain vector stores (or read-add-write) per row
+        const bool add = (p.grad_f32 & 2) != 0;
+        if (!ok) return;
+        const bool live = owner_row < p.Sq;  // (the tensor-memory loads below are warp-wide: every lane runs them)
+        float* f = reinterpret_cast<float*>(p.dq) + (int64_t)w.b * p.dqs[0] + (int64_t)w.head * p.dqs[1] +
+                   (int64_t)owner_row * p.dqs[2] + ch0;
+        if (unit == 0) {
+            if (!add && live)
+                for (int d = 0; d < kHalf && ch0 + d < p.D; d += 4)
+                    *reinterpret_cast<float4*>(f + d) = make_float4(0.f, 0.f, 0.f, 0.f);
+            return;
+        }
+        if (!mbar_wait(&sh.final_done, 0, abort_word, 150)) return;
+        tc_fence_after();
+        constexpr int kStepF = kHalf < 32 ? 16 : 32;
+#pragma unroll
+        for (int c = 0; c < kHalf; c += kStepF) {
+            uint32_t v[kStepF];
+            tmem_ld(lane_base + kColGrad + ch0 + c, v);
+            tmem_wait_ld();
+            put_f32(f + c, v, live ? p.D - ch0 - c : 0, p.scale, add);
+        }
+        return;
+    }
     if (unit == 0) {
         // no visible work for this query tile: the gradient is exactly zero
         if (ok && out)

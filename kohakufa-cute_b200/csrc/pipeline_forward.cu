@@ -401,7 +401,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
         }
         if ((threadIdx.x & 127) == 0) PH_FLUSH(t);
         // epilogue: wait for the last product, normalise, store
-        if (ok && iter == 0 && row < p.Sq && n_t[t] > 0) {
+        if (ok && iter == 0 && row < p.Sq && n_t[t] > 0 && !p.running) {
             // every key tile of this row is hidden: zero output, empty statistics
             using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
             T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] + (int64_t)row * p.os[2];
@@ -412,7 +412,46 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                 p.logsum[si] = 0.f;
             }
         }
-        if (iter > 0) {
+        if (iter > 0 && p.running) {
+            // Block of a longer key sequence: fold (accumulator, maximum, sum) into the caller's running FP32 state
+            // with the (maximum, sum) merge of the reference's split forward (split_forward.py:219-245); nothing is
+            // rounded to the 16-bit type and nothing is divided here.
+            if (ok) ok = mbar_wait(&sh.s_ready[t], iter & 1, abort_word, 32 + t);
+            if (ok) {
+                // (every lane runs the tensor-memory loads, which are warp-wide; rows beyond the sequence end
+                // only skip the global accesses)
+                tc_fence_after();
+                const bool live = row < p.Sq;
+                const int64_t si = (int64_t)b * p.ss[0] + (int64_t)h * p.ss[1] + (live ? row : 0);
+                const float m_old = live ? p.maximum[si] : -INFINITY, l_old = live ? p.run_sum[si] : 0.f;
+                const float m_new = fmaxf(m_old, m_true);
+                const float w_old = m_old == -INFINITY ? 0.f : ex2((m_old - m_new) * c2);
+                const float w_blk = m_used == -INFINITY ? 0.f : ex2((m_used - m_new) * c2);
+                float* arow = reinterpret_cast<float*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] +
+                              (int64_t)row * p.os[2];
+#pragma unroll
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(o_addr + c, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        if (live && c + i < p.D) {
+                            float4 a = *reinterpret_cast<float4*>(arow + c + i);
+                            a.x = a.x * w_old + __uint_as_float(r[i]) * w_blk;
+                            a.y = a.y * w_old + __uint_as_float(r[i + 1]) * w_blk;
+                            a.z = a.z * w_old + __uint_as_float(r[i + 2]) * w_blk;
+                            a.w = a.w * w_old + __uint_as_float(r[i + 3]) * w_blk;
+                            *reinterpret_cast<float4*>(arow + c + i) = a;
+                        }
+                    }
+                }
+                if (live) {
+                    p.maximum[si] = m_new;
+                    p.run_sum[si] = l_old * w_old + l * w_blk;
+                }
+            }
+        } else if (iter > 0) {
             if (ok) ok = mbar_wait(&sh.s_ready[t], iter & 1, abort_word, 32 + t);
             if (ok) {
                 tc_fence_after();
@@ -479,7 +518,10 @@ cudaError_t launch_t(const AttnParams& p, cudaStream_t st) {
     if (!encode_bhsd_map(&maps.q, p.q, dt, p.D, p.Sq, p.Hq, p.B, p.qs, 64, kTileQ)) return cudaErrorInvalidValue;
     if (!encode_bhsd_map(&maps.k, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kTileK)) return cudaErrorInvalidValue;
     if (!encode_bhsd_map(&maps.v, p.v, dt, p.D, p.Sk, p.Hkv, p.B, p.vs, 64, kTileK)) return cudaErrorInvalidValue;
-    if (!encode_bhsd_map(&maps.o, p.out, dt, p.D, p.Sq, p.Hq, p.B, p.os, 64, kTileQ)) return cudaErrorInvalidValue;
+    if (p.running)
+        maps.o = maps.q;  // not used: the running state is written with plain stores
+    else if (!encode_bhsd_map(&maps.o, p.out, dt, p.D, p.Sq, p.Hq, p.B, p.os, 64, kTileQ))
+        return cudaErrorInvalidValue;
     const int64_t grid = (int64_t)((p.Sq + 2 * kTileQ - 1) / (2 * kTileQ)) * p.B * p.Hq;
     kernel<<<(unsigned)grid, kThreads, Cfg::kSmemBytes, st>>>(maps, p);
     return cudaGetLastError();
@@ -496,7 +538,12 @@ bool pipeline_forward_supported(const AttnParams& p, bool bf16) {
     if (!tma_compatible(p.q, p.qs, p.B, p.Hq, p.Sq) || !tma_compatible(p.k, p.ks, p.B, p.Hkv, p.Sk) ||
         !tma_compatible(p.v, p.vs, p.B, p.Hkv, p.Sk))
         return false;
-    if (!tma_compatible(p.out, p.os, p.B, p.Hq, p.Sq)) return false;  // 16-byte vector stores per row
+    if (p.running) {  // FP32 rows read and written as 16-byte vectors
+        if (p.os[3] != 1 || reinterpret_cast<uintptr_t>(p.out) % 16 != 0 || p.os[0] % 4 || p.os[1] % 4 || p.os[2] % 4)
+            return false;
+    } else if (!tma_compatible(p.out, p.os, p.B, p.Hq, p.Sq)) {
+        return false;  // 16-byte vector stores per row
+    }
     return true;
 }
 

@@ -52,6 +52,10 @@ SIGNATURES = {
     "kfa_backward_workspace_bytes": (ctypes.c_size_t, [_TP, _TP]),
     "kfa_backward": (ctypes.c_int, [_TP] * 12 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float, ctypes.c_int,
                                                  ctypes.c_void_p]),
+    "kfa_forward_running": (ctypes.c_int, [_TP] * 8 + [ctypes.c_float, ctypes.c_int, ctypes.c_void_p]),
+    "kfa_finish_running": (ctypes.c_int, [_TP] * 6 + [ctypes.c_void_p]),
+    "kfa_backward_partial": (ctypes.c_int, [_TP] * 12 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float, ctypes.c_int,
+                                                         ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
     "kfa_center_keys_workspace_bytes": (ctypes.c_size_t, [_TP]),
     "kfa_center_keys": (ctypes.c_int, [_TP, _TP, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "kfa_center_keys_static_limit": (ctypes.c_size_t, []),
@@ -352,6 +356,61 @@ def neighborhood_backward(q, k, v, out, maximum, logsum, dout, spatial, window, 
                                              _int64_array(spatial), len(spatial), _int64_array(window), float(scale),
                                              _stream(q.device)))
     return dq, dk, dv
+
+
+def running_state(q):
+    """Fresh running state ``(acc, run_maximum, run_sum)`` for ``forward_running`` on queries ``q``."""
+    acc = torch.zeros(q.shape, device=q.device, dtype=torch.float32)
+    run_maximum = torch.full(q.shape[:-1], float("-inf"), device=q.device, dtype=torch.float32)
+    run_sum = torch.zeros(q.shape[:-1], device=q.device, dtype=torch.float32)
+    return acc, run_maximum, run_sum
+
+
+def forward_running(q, k, v, mask, state, scale, causal=False):
+    """Attends ``q`` to one key/value block and folds the result into ``state`` in place
+    (``kfa_forward_running``: unnormalised FP32 accumulator, running maximum and sum; nothing is rounded
+    to the 16-bit type between blocks)."""
+    lib = library()
+    q, k, v = _plain(q), _plain(k), _plain(v)
+    acc, run_maximum, run_sum = state
+    with torch.cuda.device(q.device):
+        blocks = None if mask is None else torch.empty(_blocks_shape(q, k, mask), device=q.device, dtype=torch.int32)
+        records = [describe(t) for t in (q, k, v, mask, acc, run_maximum, run_sum, blocks)]
+        _check(lib.kfa_forward_running(*[_ref(r) for r in records], float(scale), int(bool(causal)),
+                                       _stream(q.device)))
+
+
+def finish_running(state, dtype):
+    """``(out, maximum, logsum)`` of a running state: one division and one rounding per element, and the
+    statistics the backward expects.  The statistics reuse the state's own tensors."""
+    lib = library()
+    acc, run_maximum, run_sum = state
+    with torch.cuda.device(acc.device):
+        out = torch.empty(acc.shape, device=acc.device, dtype=dtype)
+        records = [describe(t) for t in (acc, run_maximum, run_sum, out, run_maximum, run_sum)]
+        _check(lib.kfa_finish_running(*[_ref(r) for r in records], _stream(acc.device)))
+    return out, run_maximum, run_sum
+
+
+def backward_partial(q, k, v, mask, maximum, logsum, dout, out, scale, causal, dq, dk, dv,
+                     accumulate_dq=True, accumulate_dkv=False):
+    """Gradient contributions of one (query block, key block) pair against the statistics of the whole
+    sequence, in FP32 (``kfa_backward_partial``): ``dq`` / ``dk`` / ``dv`` are float32 tensors (views allowed,
+    unit channel stride) that are overwritten or added to."""
+    lib = library()
+    q, k, v, dout, out = _plain(q), _plain(k), _plain(v), _plain(dout), _plain(out)
+    if not _rows_16_byte_addressable(dout):
+        dout = dout.contiguous()
+    with torch.cuda.device(q.device):
+        rq, rk = describe(q), describe(k)
+        need = lib.kfa_backward_workspace_bytes(_ref(rq), _ref(rk))
+        workspace = torch.empty(need, device=q.device, dtype=torch.uint8)
+        blocks = None if mask is None else pack_mask(q, k, mask)
+        records = [rq, rk, describe(v), describe(mask), describe(out), describe(maximum), describe(logsum),
+                   describe(dout), describe(blocks), describe(dq), describe(dk), describe(dv)]
+        _check(lib.kfa_backward_partial(*[_ref(r) for r in records], ctypes.c_void_p(workspace.data_ptr()), need,
+                                        float(scale), int(bool(causal)), int(bool(accumulate_dq)),
+                                        int(bool(accumulate_dkv)), _stream(q.device)))
 
 
 def merge_partial(acc_out, acc_maximum, acc_logsum, part_out, part_maximum, part_logsum, scale):

@@ -19,6 +19,11 @@ def pytest_configure(config):
 def pytest_collection_modifyitems(config, items):
     import torch
 
+    if config.pluginmanager.hasplugin("timeout"):
+        # a test that stops making progress ends with a stack dump instead of holding the GPU
+        for item in items:
+            if item.get_closest_marker("timeout") is None:
+                item.add_marker(pytest.mark.timeout(600))
     if torch.cuda.is_available():
         return
     skip = pytest.mark.skip(reason="no CUDA device in this process")

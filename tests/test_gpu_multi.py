@@ -42,6 +42,17 @@ def _worker(rank, world, port, result):
         errs = [float((out.float() - ref[:, :, sl].float()).abs().max())]
         for a, b in zip(grads, ref_grads):
             errs.append(float((a.float() - b[:, :, sl].float()).abs().max() / b.float().abs().max()))
+        # causal, zig-zag shards (the block-wise FP32 entry points underneath), relative L2 error per tensor
+        shard = lambda t: parallel.zigzag_shard(t, world, rank).contiguous().to(dev)
+        leaves = [shard(t).requires_grad_(True) for t in (q, k, v)]
+        out = parallel.ring_attention(*leaves, causal=True)
+        grads = torch.autograd.grad(out, leaves, shard(g))
+        full = [t.to(dev).requires_grad_(True) for t in (q, k, v)]
+        ref = kohakufa_cute.attention(*full, causal=True)
+        ref_grads = torch.autograd.grad(ref, full, g.to(dev))
+        for a, b in zip((out,) + tuple(grads), (ref,) + tuple(ref_grads)):
+            want = parallel.zigzag_shard(b, world, rank).float()
+            errs.append(float((a.float() - want).norm() / want.norm()))
         # head sharding: this rank's units give the same numbers as the same units of the full call
         begin, end = parallel.shard_heads(B, Hkv, world, rank)
         qs, ks, vs = parallel.take_head_shard(q.to(dev), k.to(dev), v.to(dev), begin, end)
@@ -62,5 +73,6 @@ def test_ring_attention_and_head_sharding_on_two_gpus():
     for rank in range(2):
         errs, same = result[rank]
         assert errs[0] < 0.02, errs
-        assert all(e < 0.03 for e in errs[1:]), errs
+        assert all(e < 0.03 for e in errs[1:4]), errs
+        assert all(e < 0.01 for e in errs[4:]), errs   # causal ring: out, dq, dk, dv
         assert same
