@@ -462,8 +462,9 @@ size_t delta_bytes(const kfa_tensor* q) {
 
 // Scratch of the wide-head backward behind the delta rows: the P_low and dS_low matrices of one pass.
 // A pass covers as many K/V heads (with their query heads) of one batch element as fit 2 GiB per matrix,
-// or the whole call when everything fits; zero when the head is not wide or a single K/V head's group
-// alone exceeds the limit (the general kernels run then).
+// or the whole call when everything fits.  When a single K/V head's group alone exceeds the limit the
+// passes also run over key ranges of that group: the matrices then hold [group, Sq, keys_per_pass] and dQ
+// is accumulated over the key ranges in an FP32 buffer behind them.  Zero when the head is not wide.
 // KFA_WIDE_MATRIX_BYTES overrides the limit (a smaller value trades workspace for more passes).
 size_t wide_matrix_limit() {
     if (const char* text = std::getenv("KFA_WIDE_MATRIX_BYTES")) {
@@ -474,9 +475,11 @@ size_t wide_matrix_limit() {
 }
 
 struct WidePlan {
-    int heads_per_pass = 0;  // K/V heads per pass; 0 = not a wide-head call
-    bool single = false;     // one pass over the whole call (all batches)
-    size_t matrix_bytes = 0; // one stored matrix of a pass
+    int heads_per_pass = 0;   // K/V heads per pass; 0 = not a wide-head call
+    bool single = false;      // one pass over the whole call (all batches)
+    int keys_per_pass = 0;    // > 0: passes over key ranges of one K/V head group (a multiple of 128)
+    size_t matrix_bytes = 0;  // one stored matrix of a pass
+    size_t dq_bytes = 0;      // FP32 dQ partial sums of one head group (key-range passes only)
 };
 
 WidePlan wide_plan(const kfa_tensor* q, const kfa_tensor* k) {
@@ -494,14 +497,27 @@ WidePlan wide_plan(const kfa_tensor* q, const kfa_tensor* k) {
         plan.matrix_bytes = all;
         return plan;
     }
-    const size_t one_group = kfa::wide_stored_bytes(1, Hq / Hkv, Sq, Sk);
-    if (one_group > kWideMatrixLimit) return plan;
+    const int64_t group = Hq / Hkv;
+    const size_t one_group = kfa::wide_stored_bytes(1, group, Sq, Sk);
+    if (one_group > kWideMatrixLimit) {
+        // key ranges of one head group: as many 128-key tiles as the limit holds, at least one
+        const int64_t tile_bytes = group * Sq * 128 * 2;
+        const int64_t tiles = std::max<int64_t>(1, (int64_t)(kWideMatrixLimit / (size_t)tile_bytes));
+        plan.heads_per_pass = 1;
+        plan.keys_per_pass = (int)std::min<int64_t>(tiles * 128, (Sk + 127) / 128 * 128);
+        plan.matrix_bytes = kfa::wide_stored_bytes(1, group, Sq, plan.keys_per_pass);
+        plan.dq_bytes = ((size_t)(group * Sq * D) * sizeof(float) + 255) / 256 * 256;
+        return plan;
+    }
     plan.heads_per_pass = (int)std::min<int64_t>(Hkv, (int64_t)(kWideMatrixLimit / one_group));
-    plan.matrix_bytes = kfa::wide_stored_bytes(1, (Hq / Hkv) * plan.heads_per_pass, Sq, Sk);
+    plan.matrix_bytes = kfa::wide_stored_bytes(1, group * plan.heads_per_pass, Sq, Sk);
     return plan;
 }
 
-size_t wide_extra_bytes(const kfa_tensor* q, const kfa_tensor* k) { return 2 * wide_plan(q, k).matrix_bytes; }
+size_t wide_extra_bytes(const kfa_tensor* q, const kfa_tensor* k) {
+    const WidePlan plan = wide_plan(q, k);
+    return 2 * plan.matrix_bytes + plan.dq_bytes;
+}
 
 // The same call restricted to batch element b and K/V heads [h0, h0 + n).
 kfa::AttnParams wide_slice(const kfa::AttnParams& p, int b, int h0, int n) {
@@ -529,6 +545,27 @@ kfa::AttnParams wide_slice(const kfa::AttnParams& p, int b, int h0, int n) {
     s.B = 1;
     s.Hq = n * g;
     s.Hkv = n;
+    return s;
+}
+
+// A pass restricted further to keys [k0, k0 + n) of its head group; `position` is 1 first, 2 middle, 3 last.
+kfa::AttnParams wide_key_range(const kfa::AttnParams& p, int k0, int n, int position, float* dq_acc) {
+    kfa::AttnParams s = p;
+    auto shift = [](const void* base, int64_t elements) {
+        return static_cast<const void*>(static_cast<const char*>(base) + elements * 2);
+    };
+    s.k = shift(p.k, (int64_t)k0 * p.ks[2]);
+    s.v = shift(p.v, (int64_t)k0 * p.vs[2]);
+    s.dk = const_cast<void*>(shift(p.dk, (int64_t)k0 * p.dks[2]));
+    s.dv = const_cast<void*>(shift(p.dv, (int64_t)k0 * p.dvs[2]));
+    if (p.has_mask) {
+        s.mask = p.mask + (int64_t)k0 * p.ms[3];
+        s.blocks = p.blocks + (int64_t)(k0 / 64) * p.bs[3];
+    }
+    s.Sk = n;
+    s.causal_shift = -k0;
+    s.dq_pass = position;
+    s.dq_acc = dq_acc;
     return s;
 }
 
@@ -748,6 +785,19 @@ int backward_impl(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v,
         };
         if (plan.single) {
             if (int e = run_pass(p)) return e;
+        } else if (plan.keys_per_pass > 0) {
+            // one head group at a time, key range by key range; dQ partial sums live behind the two matrices
+            float* dq_acc = reinterpret_cast<float*>(static_cast<char*>(stored) + 2 * plan.matrix_bytes);
+            for (int b = 0; b < p.B; ++b)
+                for (int h0 = 0; h0 < p.Hkv; ++h0) {
+                    const kfa::AttnParams group = wide_slice(p, b, h0, 1);
+                    for (int k0 = 0; k0 < p.Sk; k0 += plan.keys_per_pass) {
+                        const int n = std::min(plan.keys_per_pass, p.Sk - k0);
+                        const bool first = k0 == 0, last = k0 + n >= p.Sk;
+                        const int position = first && last ? 0 : first ? 1 : last ? 3 : 2;
+                        if (int e = run_pass(wide_key_range(group, k0, n, position, dq_acc))) return e;
+                    }
+                }
         } else {
             // the stored matrices are reused pass by pass; passes are ordered on the stream
             for (int b = 0; b < p.B; ++b)

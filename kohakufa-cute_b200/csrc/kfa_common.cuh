@@ -52,6 +52,14 @@ struct AttnParams {
     // grad_f32 bit 0: dq/dk/dv are FP32 tensors; bit 1: add to dq instead of overwriting it; bit 2: same for dk, dv.
     float* run_sum;
     int64_t ss[2];
+    // Wide-head backward in passes over key ranges (sequences whose stored score matrices exceed the workspace
+    // limit): the pass sees keys [k0, k0 + Sk) of the call, so a key is visible under a causal mask iff
+    // col <= row + causal_shift (causal_shift = -k0), and dQ accumulates over the passes in FP32:
+    // dq_pass 0 = single pass (write the 16-bit gradient), 1 = first (write dq_acc), 2 = middle (add to dq_acc),
+    // 3 = last (add dq_acc, write the 16-bit gradient).  dq_acc is [B,Hq,Sq,D] of the pass, contiguous.
+    int causal_shift;
+    int dq_pass;
+    float* dq_acc;
     int running;
     int grad_f32;
     int* status;      // device-visible status word (mapped host memory)

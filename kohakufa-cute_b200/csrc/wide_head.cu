@@ -36,22 +36,32 @@ constexpr int kChunkBytes = kTile * 128;  // 128 rows x 64 channels of a 16-bit 
 constexpr int kRing = 6;                  // 16 KB slots for streamed chunks
 constexpr float kRebase = 8.0f;
 
-// Combined state of key tile j (128 keys) from the 64-key table entries: 0 hidden, 2 visible, 1 mixed.
-__device__ __forceinline__ int key_tile_state(const AttnParams& p, int b, int h, int j) {
+// Combined state of key tile j (128 keys) for the query rows [q0, q0 + 128), from the 64x64 table entries:
+// 0 hidden, 2 visible, 1 mixed.  Masks broadcast over queries have one row of entries.
+__device__ __forceinline__ int key_tile_state(const AttnParams& p, int b, int h, int q0, int j) {
     if (!p.has_mask) return 2;
     const int nk64 = (p.Sk + 63) >> 6;
     const int32_t* base = p.blocks + (int64_t)b * p.bs[0] + (int64_t)h * p.bs[1];
-    const int s0 = base[(int64_t)(2 * j) * p.bs[3]];
-    const int s1 = (2 * j + 1 < nk64) ? base[(int64_t)(2 * j + 1) * p.bs[3]] : s0;
-    if (s0 == 0 && s1 == 0) return 0;
-    if (s0 == 2 && s1 == 2) return 2;
-    return 1;
+    int r0 = 0, r1 = 0;
+    if (p.bs[2] != 0) {
+        r0 = q0 >> 6;
+        r1 = (min(q0 + kTile, p.Sq) - 1) >> 6;
+    }
+    const int c1 = min(2 * j + 1, nk64 - 1);
+    bool any = false, all = true;
+    for (int r = r0; r <= r1; ++r)
+        for (int c = 2 * j; c <= c1; ++c) {
+            const int s = base[(int64_t)r * p.bs[2] + (int64_t)c * p.bs[3]];
+            any = any || s != 0;
+            all = all && s == 2;
+        }
+    return all ? 2 : (any ? 1 : 0);
 }
 
 // Key tiles a 128-row query tile starting at q0 may see.
 __device__ __forceinline__ int key_tiles_of(const AttnParams& p, int q0) {
     const int row_hi = min(p.Sq, q0 + kTile);
-    const int k_hi = p.causal ? min(p.Sk, row_hi) : p.Sk;
+    const int k_hi = p.causal ? max(0, min(p.Sk, row_hi + p.causal_shift)) : p.Sk;
     return (k_hi + kTile - 1) / kTile;
 }
 
@@ -142,7 +152,7 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
             int pos = 0;
             bool ok = true;
             for (int j = 0; j < n_tiles && ok; ++j) {
-                if (key_tile_state(p, b, h, j) == 0) continue;
+                if (key_tile_state(p, b, h, q0, j) == 0) continue;
                 // the K chunks of the tile, then the V chunks of this CTA's channel half
                 for (int i = 0; i < chunks + hc && ok; ++i, ++pos) {
                     if ((pos & 1) != me) continue;
@@ -175,7 +185,7 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
             bool ok = mbar_wait(&sh.q_full, 0, abort_word, 20);
             int pos = 0, iter = 0;
             for (int j = 0; j < n_tiles && ok; ++j) {
-                if (key_tile_state(p, b, h, j) == 0) continue;
+                if (key_tile_state(p, b, h, q0, j) == 0) continue;
                 // S_a also holds P_low of the previous tile, which issuer 1's product is still reading
                 if (who == 0 && iter > 0) ok = mbar_wait(&sh.pvb_done, (iter - 1) & 1, abort_word, 24);
                 for (int c = 0; c < chunks && ok; ++c, ++pos) {
@@ -221,12 +231,15 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
         const int width = 64 * hc;  // output channels of this CTA
         const float c2 = fabsf(p.scale) * kLog2e;
         const uint64_t c2_pair = f2_pack(c2, c2);
-        const uint8_t* kmask = p.has_mask ? p.mask + (int64_t)b * p.ms[0] + (int64_t)h * p.ms[1] : nullptr;
+        // this row's line of the mask (every row shares one line when the mask is broadcast over queries)
+        const uint8_t* kmask = p.has_mask ? p.mask + (int64_t)b * p.ms[0] + (int64_t)h * p.ms[1] +
+                                                (int64_t)min(row, p.Sq - 1) * p.ms[2]
+                                          : nullptr;
         float m_used = -INFINITY, m_true = -INFINITY, l = 0.f;
         int iter = 0;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
-            const int state = key_tile_state(p, b, h, j);
+            const int state = key_tile_state(p, b, h, q0, j);
             if (state == 0) continue;
             ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 30);
             if (!ok) break;
@@ -243,7 +256,7 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
             }
             const int key0 = j * kTile;
             int lim = p.Sk - key0;
-            if (p.causal) lim = min(lim, row - key0 + 1);
+            if (p.causal) lim = min(lim, row + p.causal_shift - key0 + 1);
             if (lim < kTile) {
 #pragma unroll
                 for (int c = 0; c < kTile; ++c) s[c] = c < lim ? s[c] : -INFINITY;
@@ -499,7 +512,9 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
                 row_dl = p.delta[si];
             }
         }
-        const uint8_t* kmask = p.has_mask ? p.mask + (int64_t)b * p.ms[0] + (int64_t)h * p.ms[1] : nullptr;
+        const uint8_t* kmask = p.has_mask ? p.mask + (int64_t)b * p.ms[0] + (int64_t)h * p.ms[1] +
+                                                (int64_t)min(row, p.Sq - 1) * p.ms[2]
+                                          : nullptr;
         const int64_t row_off = (((int64_t)b * p.Hq + h) * p.Sq + (row_ok ? row : 0)) * st.pitch;
         uint16_t* p_row = reinterpret_cast<uint16_t*>(st.p_low) + row_off;
         uint16_t* ds_row = reinterpret_cast<uint16_t*>(st.ds_low) + row_off;
@@ -530,8 +545,8 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
             if (!row_ok) continue;
             if (MODE == 0) {
                 int lim = p.Sk - key0;
-                if (p.causal) lim = min(lim, row - key0 + 1);
-                const int state = key_tile_state(p, b, h, j);
+                if (p.causal) lim = min(lim, row + p.causal_shift - key0 + 1);
+                const int state = key_tile_state(p, b, h, q0, j);
                 const uint64_t m_pair = f2_pack(row_m, row_m), l_pair = f2_pack(row_ls, row_ls);
 #pragma unroll
                 for (int c = 0; c < kTile; c += 8) {
@@ -633,7 +648,7 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Grad
     // streamed tile range and the number of passes over it (query heads of the group)
     int first = 0, end, passes = 1;
     if (KV) {
-        first = p.causal ? blk : 0;
+        first = p.causal ? max(0, (owner0 - p.causal_shift) / kTile) : 0;  // first query tile that sees these keys
         end = (p.Sq + kTile - 1) / kTile;
         passes = p.group;
     } else {
@@ -717,9 +732,21 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Grad
         T* out = reinterpret_cast<T*>(base) + (int64_t)b * os[0] + (int64_t)head * os[1] + (int64_t)row * os[2] +
                  half * width;
         const float mul = which == 2 ? 1.f : p.scale;
+        // dQ of a call that runs in passes over key ranges: FP32 partial sums between the passes
+        const int pass = which == 0 ? p.dq_pass : 0;
+        float* part = pass ? p.dq_acc + (((int64_t)b * p.Hq + head) * p.Sq + min(row, p.Sq - 1)) * p.D + half * width
+                           : nullptr;
         if (units == 0) {
-            if (row < owner_len)
-                for (int d = 0; d < width; d += 8) *reinterpret_cast<uint4*>(out + d) = make_uint4(0, 0, 0, 0);
+            if (row < owner_len) {
+                if (pass == 0) {
+                    for (int d = 0; d < width; d += 8) *reinterpret_cast<uint4*>(out + d) = make_uint4(0, 0, 0, 0);
+                } else if (pass == 1) {
+                    for (int d = 0; d < width; d += 4) *reinterpret_cast<float4*>(part + d) = make_float4(0.f, 0.f, 0.f, 0.f);
+                } else if (pass == 3) {
+                    for (int d = 0; d < width; d += 2)
+                        *reinterpret_cast<uint32_t*>(out + d) = pack2<BF16>(part[d], part[d + 1]);
+                }
+            }
         } else if (mbar_wait(&sh.done, 0, abort_word, 52)) {
             tc_fence_after();
             const uint32_t acc = tmem + (static_cast<uint32_t>(warp * 32) << 16);
@@ -727,7 +754,31 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Grad
                 uint32_t v[32];
                 tmem_ld32(acc + c, v);
                 tmem_wait_ld();
-                if (row < owner_len) {
+                if (pass != 0 && row < owner_len) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        float x = __uint_as_float(v[e]) * mul;
+                        if (pass != 1) x += part[c + e];
+                        v[e] = __float_as_uint(x);
+                    }
+                    if (pass != 3) {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4)
+                            *reinterpret_cast<float4*>(part + c + e) =
+                                make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
+                                            __uint_as_float(v[e + 3]));
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 8) {
+                            uint4 o;
+                            o.x = pack2<BF16>(__uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+                            o.y = pack2<BF16>(__uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+                            o.z = pack2<BF16>(__uint_as_float(v[e + 4]), __uint_as_float(v[e + 5]));
+                            o.w = pack2<BF16>(__uint_as_float(v[e + 6]), __uint_as_float(v[e + 7]));
+                            *reinterpret_cast<uint4*>(out + c + e) = o;
+                        }
+                    }
+                } else if (row < owner_len) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
                         uint4 o;
@@ -782,7 +833,6 @@ bool wide_common(const AttnParams& p) {
     if (p.D != 256 && p.D != 384 && p.D != 512) return false;
     if (p.nd != 0) return false;
     if (p.scale == 0.f || p.Sk < 2) return false;  // exact-zero guarantees of those cases live in the general kernels
-    if (p.has_mask && p.ms[2] != 0) return false;  // only masks broadcast over the query axis
     return tma_compatible(p.q, p.qs, p.B, p.Hq, p.Sq) && tma_compatible(p.k, p.ks, p.B, p.Hkv, p.Sk) &&
            tma_compatible(p.v, p.vs, p.B, p.Hkv, p.Sk);
 }

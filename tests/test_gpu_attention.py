@@ -102,15 +102,24 @@ def test_wide_head_shapes(shape, dtype):
 
 
 @pytest.mark.parametrize("scale", (-0.05, 0.2))
-@pytest.mark.parametrize("name", ("keys", "key_padding", "all_false"))
+@pytest.mark.parametrize("name", ("keys", "key_padding", "all_false", "full2d", "per_head"))
 def test_wide_head_masks_and_scales(name, scale):
     B, Hq, Hkv, Sq, Sk, D = 2, 4, 2, 150, 330, 256
     gen = torch.Generator().manual_seed(77)
     mask = _mask_variants(B, Hq, Sq, Sk, gen)[name].cuda()
     q, k, v, dout = make_inputs(B, Hq, Hkv, Sq, Sk, D, torch.bfloat16, seed=78)
+    expanded = mask.expand(B, Hq, Sq, Sk)
+    assert native().selected_family(q, k, v, expanded, True) == 2   # every mask shape stays on the wide-head kernels
+    assert native().selected_family(q, k, v, expanded, True, backward=True) == 2
     actual = run_attention(api().attention, q, k, v, dout, mask=mask, causal=True, scale=scale)
     check_against_oracle(actual, q, k, v, dout, mask, True, scale)
-    if name != "all_false":
+    if name in ("full2d", "per_head"):
+        seen = ao.visible_pairs(B, Hq, Sq, Sk, mask.cpu(), True)
+        hidden = ~seen.any(-1)
+        if bool(hidden.any()):  # all-hidden rows give exactly zero output and zero dQ
+            assert float(actual[0].cpu()[hidden].abs().max()) == 0
+            assert float(actual[1].cpu()[hidden].abs().max()) == 0
+    elif name != "all_false":
         hidden_keys = ~mask.expand(B, 1, 1, Sk)[:, 0, 0].cpu()
         for grad in actual[2:]:
             assert float(grad.cpu()[hidden_keys[:, None, :].expand(B, Hkv, Sk)].abs().max()) == 0
@@ -128,10 +137,28 @@ def test_wide_head_backward_in_head_group_passes(monkeypatch):
     split = run_attention(api().attention, q, k, v, dout, causal=True)
     for a, b in zip(whole, split):
         assert torch.equal(a, b)
-    monkeypatch.setenv("KFA_WIDE_MATRIX_BYTES", str(one_group - 256))
-    assert native().selected_family(q, k, v, None, True, backward=True) == 0  # not even one group fits
-    monkeypatch.delenv("KFA_WIDE_MATRIX_BYTES")
     check_against_oracle(split, q, k, v, dout, None, True, None)
+    # not even one group fits: passes over key ranges of a group, dQ summed over the ranges in FP32
+    for limit in (one_group - 256, 1):  # two ranges (256 + 44 keys) and three (128 + 128 + 44)
+        monkeypatch.setenv("KFA_WIDE_MATRIX_BYTES", str(limit))
+        assert native().selected_family(q, k, v, None, True, backward=True) == 2
+        ranged = run_attention(api().attention, q, k, v, dout, causal=True)
+        assert torch.equal(ranged[0], whole[0])
+        assert torch.equal(ranged[2], whole[2]) and torch.equal(ranged[3], whole[3])  # key owners: same sums
+        torch.testing.assert_close(ranged[1], whole[1], atol=2e-3, rtol=2e-2)
+        check_against_oracle(ranged, q, k, v, dout, None, True, None)
+    # the same with a per-head mask (the tile table and the mask are addressed from the range's first key) and
+    # with more keys than queries (the last range is hidden from every query under the causal mask)
+    B, Hq, Hkv, Sq, Sk = 1, 2, 1, 200, 450
+    gen = torch.Generator().manual_seed(81)
+    q, k, v, dout = make_inputs(B, Hq, Hkv, Sq, Sk, D, torch.float16, seed=82)
+    for mask, causal in ((torch.rand(B, Hq, Sq, Sk, generator=gen) > 0.4, False), (None, True),
+                         ((torch.arange(Sk)[None, :] // 150 == torch.arange(Sq)[:, None] // 100)[None, None], False)):
+        mask = None if mask is None else mask.cuda()
+        monkeypatch.setenv("KFA_WIDE_MATRIX_BYTES", "1")
+        ranged = run_attention(api().attention, q, k, v, dout, mask=mask, causal=causal)
+        monkeypatch.delenv("KFA_WIDE_MATRIX_BYTES")
+        check_against_oracle(ranged, q, k, v, dout, mask, causal, None)
 
 
 def test_wide_head_projection_layout():
@@ -247,16 +274,17 @@ def test_boolean_masks(name, causal, D):
         assert float(actual[1].cpu()[hidden].abs().max()) == 0
 
 
-def test_block_sparse_full_mask_long_sequence():
+@pytest.mark.parametrize("D", (128, 256))
+def test_block_sparse_full_mask_long_sequence(D):
     """A full [Sq, Sk] mask with hidden, mixed and visible 128x128 blocks (a banded document mask with ragged
     edges) at a length where tile skipping matters; per-head variation through a second, shifted band."""
-    B, H, S, D = 1, 2, 1536, 128
+    B, H, S = 1, 2, 1536
     q, k, v, dout = make_inputs(B, H, H, S, S, D, torch.bfloat16, seed=6)
     idx = torch.arange(S)
     band0 = (idx[:, None] // 200 == idx[None, :] // 200)           # documents of 200 tokens
     band1 = ((idx[:, None] - idx[None, :]).abs() < 333)            # a sliding band
     mask = torch.stack([band0, band1])[None].cuda()                # [1, H, S, S]
-    assert native().selected_family(q, k, v, mask, True) == 1
+    assert native().selected_family(q, k, v, mask, True) == (1 if D == 128 else 2)
     actual = run_attention(api().attention, q, k, v, dout, mask=mask, causal=True)
     check_against_oracle(actual, q, k, v, dout, mask, True, None)
 
@@ -659,8 +687,6 @@ def _random_case(index):
     Sk = int(torch.randint(2, 420, (1,), generator=gen))
     causal = bool(torch.randint(2, (1,), generator=gen))
     kind = pick(("none", "none", "keys", "full2d", "per_head", "banded"))
-    if D >= 256 and kind not in ("none", "keys"):
-        kind = "keys"  # the wide-head family serves masks broadcast over queries; others go to the general kernels
     dtype = pick((torch.bfloat16, torch.float16))
     scale = pick((None, None, -0.11, 0.3))
     return B, Hkv * group, Hkv, Sq, Sk, D, causal, kind, dtype, scale, gen

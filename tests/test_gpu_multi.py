@@ -39,9 +39,14 @@ def _worker(rank, world, port, result):
         full = [t.to(dev).requires_grad_(True) for t in (q, k, v)]
         ref = kohakufa_cute.attention(*full, mask=mask.to(dev))
         ref_grads = torch.autograd.grad(ref, full, g.to(dev))
-        errs = [float((out.float() - ref[:, :, sl].float()).abs().max())]
+        def per_head(got, want):
+            """Largest relative L2 error over the (batch, head) slices (the operator's own 1 % gate)."""
+            diff = (got.float() - want.float()).flatten(2).norm(dim=2)
+            return float((diff / want.float().flatten(2).norm(dim=2)).max())
+
+        errs = [per_head(out, ref[:, :, sl])]
         for a, b in zip(grads, ref_grads):
-            errs.append(float((a.float() - b[:, :, sl].float()).abs().max() / b.float().abs().max()))
+            errs.append(per_head(a, b[:, :, sl]))
         # causal, zig-zag shards (the block-wise FP32 entry points underneath), relative L2 error per tensor
         shard = lambda t: parallel.zigzag_shard(t, world, rank).contiguous().to(dev)
         leaves = [shard(t).requires_grad_(True) for t in (q, k, v)]
@@ -51,8 +56,7 @@ def _worker(rank, world, port, result):
         ref = kohakufa_cute.attention(*full, causal=True)
         ref_grads = torch.autograd.grad(ref, full, g.to(dev))
         for a, b in zip((out,) + tuple(grads), (ref,) + tuple(ref_grads)):
-            want = parallel.zigzag_shard(b, world, rank).float()
-            errs.append(float((a.float() - want).norm() / want.norm()))
+            errs.append(per_head(a, parallel.zigzag_shard(b, world, rank)))
         # head sharding: this rank's units give the same numbers as the same units of the full call
         begin, end = parallel.shard_heads(B, Hkv, world, rank)
         qs, ks, vs = parallel.take_head_shard(q.to(dev), k.to(dev), v.to(dev), begin, end)
@@ -72,7 +76,6 @@ def test_ring_attention_and_head_sharding_on_two_gpus():
     mp.spawn(_worker, args=(2, _free_port(), result), nprocs=2, join=True)
     for rank in range(2):
         errs, same = result[rank]
-        assert errs[0] < 0.02, errs
-        assert all(e < 0.03 for e in errs[1:4]), errs
-        assert all(e < 0.01 for e in errs[4:]), errs   # causal ring: out, dq, dk, dv
+        # masked ring, then causal ring: out, dq, dk, dv per head against the unsharded operator
+        assert all(e < 0.01 for e in errs), errs
         assert same
