@@ -31,7 +31,11 @@ using namespace na;
 constexpr int kTile = 128;
 constexpr int kChunkBytes = kTile * 128;  // 128 rows x 64 channels, 16-bit
 constexpr int kRing = 5;
-constexpr float kRebase = 8.0f;
+// The accumulator is re-based when the row maximum has grown by more than this power of two in probability terms:
+// probabilities against the stale maximum stay inside FP16 (2^14) or BF16's FP32 range (2^32), and the round trip of
+// the accumulator through registers stays rare also for large logits.
+template <bool BF16>
+__host__ __device__ constexpr float rebase_limit() { return BF16 ? 32.0f : 14.0f; }
 
 struct NaMaps {
     CUtensorMap q, k, v, g;
@@ -199,7 +203,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
             const float mx = fmaxf(mx0, mx1);
             tmem_wait_st();
             m_true = fmaxf(m_true, mx);
-            const bool rebase = mx > m_used && (m_used == -INFINITY || (mx - m_used) * c2 > kRebase);
+            const bool rebase = mx > m_used && (m_used == -INFINITY || (mx - m_used) * c2 > rebase_limit<BF16>());
             float alpha = 1.f;
             if (rebase) {
                 alpha = (m_used == -INFINITY) ? 0.f : ex2((m_used - mx) * c2);

@@ -38,7 +38,12 @@ namespace {
 constexpr int kTileQ = 128;
 constexpr int kTileK = 128;
 constexpr int kThreads = 384;  // three warpgroups: softmax 0, softmax 1, (MMA, loader, 2 idle warps)
-constexpr float kRebase = 8.0f;  // re-base the accumulator when the maximum grows by > 2^8
+// The accumulator is re-based when the row maximum has grown by more than 2^kRebase in probability terms.  Until then
+// probabilities are formed against the stale maximum and may reach 2^kRebase: 2^14 stays inside FP16, and BF16 has
+// FP32's range (row sums stay below 2^32 * keys, far inside FP32).  Re-basing costs a round trip of the output
+// accumulator through registers on the softmax's critical path, so it should be rare also for large logits.
+template <bool BF16>
+__host__ __device__ constexpr float rebase_limit() { return BF16 ? 32.0f : 14.0f; }
 constexpr int kMaxKeyTiles = 4096;  // masked calls keep one state byte per key tile in shared memory
 
 template <int D>
@@ -344,7 +349,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
             }
             const float mx = max3(mx0, mx1, fmaxf(s[kTileK - 2], s[kTileK - 1]));
             m_true = fmaxf(m_true, mx);
-            const bool rebase = mx > m_used && (m_used == -INFINITY || (mx - m_used) * c2 > kRebase);
+            const bool rebase = mx > m_used && (m_used == -INFINITY || (mx - m_used) * c2 > rebase_limit<BF16>());
             float alpha = 1.f;
             if (rebase) {
                 alpha = (m_used == -INFINITY) ? 0.f : ex2((m_used - mx) * c2);

@@ -34,7 +34,11 @@ namespace {
 constexpr int kTile = 128;
 constexpr int kChunkBytes = kTile * 128;  // 128 rows x 64 channels of a 16-bit type (one TMA box)
 constexpr int kRing = 6;                  // 16 KB slots for streamed chunks
-constexpr float kRebase = 8.0f;
+// The accumulator is re-based when the row maximum has grown by more than this power of two in probability terms:
+// probabilities against the stale maximum stay inside FP16 (2^14) or BF16's FP32 range (2^32), and the round trip of
+// the accumulator through registers stays rare also for large logits.
+template <bool BF16>
+__host__ __device__ constexpr float rebase_limit() { return BF16 ? 32.0f : 14.0f; }
 
 // Combined state of key tile j (128 keys) for the query rows [q0, q0 + 128), from the 64x64 table entries:
 // 0 hidden, 2 visible, 1 mixed.  Masks broadcast over queries have one row of entries.
@@ -276,7 +280,7 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
             }
             const float mx = max3(mx0, mx1, fmaxf(s[kTile - 2], s[kTile - 1]));
             m_true = fmaxf(m_true, mx);
-            const bool rebase = mx > m_used && (m_used == -INFINITY || (mx - m_used) * c2 > kRebase);
+            const bool rebase = mx > m_used && (m_used == -INFINITY || (mx - m_used) * c2 > rebase_limit<BF16>());
             float alpha = 1.f;
             if (rebase) {
                 alpha = (m_used == -INFINITY) ? 0.f : ex2((m_used - mx) * c2);
