@@ -64,7 +64,7 @@ struct Shared {
     uint64_t kv_full[6];
     uint64_t kv_empty[6];
     uint64_t s_ready[2];
-    uint64_t p_ready[2];
+    uint64_t p_half[2][2];  // [tile][half of the keys]: those probabilities of the tile are in tensor memory
     uint64_t o_staged[2];  // every softmax thread of the tile has put its output row into shared memory
     uint32_t tmem_base;
     int abort_word;
@@ -143,7 +143,8 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&sh.s_ready[t], 1);
-            mbar_init(&sh.p_ready[t], kTileQ);
+            mbar_init(&sh.p_half[t][0], kTileQ);
+            mbar_init(&sh.p_half[t][1], kTileQ);
             mbar_init(&sh.o_staged[t], kTileQ);
         }
         mbar_fence_init();
@@ -217,10 +218,12 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                             idesc_s, kk > 0);
                 }
             };
-            auto issue_o = [&](int t, int slot, bool accumulate) {
+            // P*V over one half of the tile's keys (the half whose probabilities have been handed over: the first
+            // half of the product runs while the softmax still forms the second half of the probabilities)
+            auto issue_o = [&](int t, int slot, int half, bool accumulate) {
                 const uint32_t b0 = slot * Cfg::kTileBytes;
 #pragma unroll
-                for (int kk = 0; kk < kTileK / 16; ++kk)
+                for (int kk = half * (kTileK / 32); kk < (half + 1) * (kTileK / 32); ++kk)
                     umma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, umma_desc_advance(v_desc, b0 + kk * 2048),
                             idesc_o, accumulate || kk > 0);
             };
@@ -261,11 +264,17 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                 bool k_waited = false;
                 for (int t = 0; t < 2 && ok; ++t) {
                     if (j >= n_t[t]) continue;
-                    ok = mbar_wait(&sh.p_ready[t], iter[t] & 1, abort_word, 23 + t);
+                    ok = mbar_wait(&sh.p_half[t][0], iter[t] & 1, abort_word, 23 + t);
                     if (!ok) break;
                     PH(1);
                     tc_fence_after();
-                    issue_o(t, v_slot, iter[t] > 0);
+                    issue_o(t, v_slot, 0, iter[t] > 0);
+                    PH(2);
+                    ok = mbar_wait(&sh.p_half[t][1], iter[t] & 1, abort_word, 26 + t);
+                    if (!ok) break;
+                    PH(1);
+                    tc_fence_after();
+                    issue_o(t, v_slot, 1, true);
                     PH(2);
                     if (jn < n_t[t]) {
                         if (!k_waited) {
@@ -341,13 +350,19 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                     s[c] = kmask[(int64_t)key * p.ms[3]] != 0 ? s[c] : -INFINITY;
                 }
             }
+            // four independent chains of three-input maxima
             float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
+            float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
 #pragma unroll
-            for (int c = 6; c < kTileK - 2; c += 4) {
+            for (int c = 12; c < kTileK - 4; c += 8) {
                 mx0 = max3(mx0, s[c], s[c + 1]);
                 mx1 = max3(mx1, s[c + 2], s[c + 3]);
+                mx2 = max3(mx2, s[c + 4], s[c + 5]);
+                mx3 = max3(mx3, s[c + 6], s[c + 7]);
             }
-            const float mx = max3(mx0, mx1, fmaxf(s[kTileK - 2], s[kTileK - 1]));
+            mx0 = max3(mx0, s[kTileK - 4], s[kTileK - 3]);
+            mx1 = max3(mx1, s[kTileK - 2], s[kTileK - 1]);
+            const float mx = fmaxf(max3(mx0, mx1, mx2), mx3);
             m_true = fmaxf(m_true, mx);
             const bool rebase = mx > m_used && (m_used == -INFINITY || (mx - m_used) * c2 > rebase_limit<BF16>());
             float alpha = 1.f;
@@ -390,6 +405,11 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                     w[i + 1] = pack2<BF16>(pc, pd);
                 }
                 tmem_st16(s_addr + c / 2, w);
+                if (c == kTileK / 2 - 32) {  // the first half of the keys is done: hand it over
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(&sh.p_half[t][0]);
+                }
             }
             {
                 float x0, x1, x2, x3;
@@ -400,7 +420,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
             PH(3);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&sh.p_ready[t]);
+            mbar_arrive(&sh.p_half[t][1]);
             PH(4);
             ++iter;
         }
