@@ -82,9 +82,23 @@ __device__ __forceinline__ void consumer_role(const Maps& maps, const AttnParams
                 }
                 pw[c / 2] = pack2<BF16>(pa, pb);
             };
+            // Both consumer warpgroups form probabilities at the same time, and together they ask the
+            // special-function unit for one result per score: where no score is hidden (no mask, every streamed
+            // query inside the sequence), every fourth pair is evaluated on the FMA and integer pipes instead.
+            auto prob_poly = [&](int c) {
+                float pa, pb;
+                ex2_poly_pair(f2_mul(f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), c2_pair), pa, pb);
+                pw[c / 2] = pack2<BF16>(pa, pb);
+            };
             if (masked) {
 #pragma unroll
                 for (int c = 0; c < kCols; c += 2) prob(c, true);
+            } else if (!p.has_mask && col0 + kCols <= p.Sq) {
+#pragma unroll
+                for (int c = 0; c < kCols; c += 2) {
+                    if ((c & 6) == 6) prob_poly(c);
+                    else prob(c, false);
+                }
             } else {
 #pragma unroll
                 for (int c = 0; c < kCols; c += 2) prob(c, false);

@@ -41,6 +41,8 @@ __device__ __forceinline__ void consumer_role(const Maps& maps, const AttnParams
                                                  (int64_t)min(owner_row, p.Sq - 1) * p.ms[2]
                                            : nullptr;
 
+    // every row of this warp has visible keys (no mask, no row beyond the sequence end): statistics are finite
+    const bool rows_real = !p.has_mask && __all_sync(0xffffffffu, owner_row < p.Sq && row_m != INFINITY);
     int g, i;
     w.begin(p, g, i);
     int unit = 0;
@@ -86,9 +88,24 @@ __device__ __forceinline__ void consumer_role(const Maps& maps, const AttnParams
                 }
                 pw[c / 2] = pack2<BF16>(pa, pb);
             };
+            // Both consumer warpgroups form probabilities at the same time, and together they ask the
+            // special-function unit for one result per score: where no score is hidden, every fourth pair is
+            // evaluated on the FMA and integer pipes instead.
+            auto prob_poly = [&](int c) {
+                float pa, pb;
+                ex2_poly_pair(f2_sub(f2_mul(f2_sub(f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), m_pair),
+                                            c2_pair), ls_pair), pa, pb);
+                pw[c / 2] = pack2<BF16>(pa, pb);
+            };
             if (masked) {
 #pragma unroll
                 for (int c = 0; c < kCols; c += 2) prob(c, true);
+            } else if (rows_real) {
+#pragma unroll
+                for (int c = 0; c < kCols; c += 2) {
+                    if ((c & 6) == 6) prob_poly(c);
+                    else prob(c, false);
+                }
             } else {
 #pragma unroll
                 for (int c = 0; c < kCols; c += 2) prob(c, false);

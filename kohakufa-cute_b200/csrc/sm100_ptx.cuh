@@ -299,6 +299,36 @@ __device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
     asm("mul.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// 2^x for a packed pair on the FMA and integer pipes instead of the special-function unit (16 results per
+// cycle and SM, which is what two consumer warpgroups forming probabilities at the same time wait for):
+// x = n + r with n = round(x), |r| <= 1/2, 2^r by a degree-4 polynomial (relative error below 1e-5, far
+// finer than the 16-bit probabilities), and n added to the exponent field.  Arguments must not be NaN; they are
+// clamped at -126, so results below 2^-126 come out as about 2^-126 instead of zero: callers use it only where no
+// score is hidden.
+__device__ __forceinline__ void ex2_poly_pair(uint64_t x, float& lo, float& hi) {
+    float xa, xb;
+    f2_unpack(x, xa, xb);
+    x = f2_pack(fmaxf(xa, -126.f), fmaxf(xb, -126.f));
+    const uint64_t magic = f2_pack(12582912.f, 12582912.f);  // 1.5 * 2^23: the sum's low mantissa bits hold n
+    const uint64_t t = f2_add(x, magic);
+    const uint64_t r = f2_sub(x, f2_sub(t, magic));
+    uint64_t q = f2_fma(r, f2_pack(0.009235221892595291f, 0.009235221892595291f),
+                        f2_pack(0.05584758520126343f, 0.05584758520126343f));
+    q = f2_fma(q, r, f2_pack(0.24031522870063782f, 0.24031522870063782f));
+    q = f2_fma(q, r, f2_pack(0.6931316256523132f, 0.6931316256523132f));
+    q = f2_fma(q, r, f2_pack(0.9999977946281433f, 0.9999977946281433f));
+    float qa, qb, ta, tb;
+    f2_unpack(q, qa, qb);
+    f2_unpack(t, ta, tb);
+    lo = __int_as_float(__float_as_int(qa) + (__float_as_int(ta) << 23));
+    hi = __int_as_float(__float_as_int(qb) + (__float_as_int(tb) << 23));
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float r;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
