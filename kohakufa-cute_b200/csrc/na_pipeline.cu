@@ -70,6 +70,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
     const int64_t bh = blockIdx.x / nblk;
     const int h = (int)(bh % p.Hq), b = (int)(bh / p.Hq);
     const int q0 = qblk * kTile;
+    PH_DECL;
 
     if (threadIdx.x == 0) {
         sh.abort_word = *reinterpret_cast<volatile int*>(p.abort_flag) != 0 ? 90 : 0;  // 90: an earlier CTA gave up
@@ -173,11 +174,14 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
         float m_used = -INFINITY, m_true = -INFINITY, l = 0.f;
         int iter = 0;
         bool ok = true;
+        PH(6);
         for (int j = next_tile(sh.bitmap, 0); j >= 0 && ok; j = next_tile(sh.bitmap, j + 1)) {
             uint32_t vis[4] = {0, 0, 0, 0};
             if (row_ok) box_mask<4>(p, box, j * kTile, p.Sk, vis);
+            PH(5);
             ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 30);
             if (!ok) break;
+            PH(0);
             tc_fence_after();
             // pass 1: hide what the row does not see (written back as -inf), maximum of the rest
             // 32-column chunks that no row of this warp can see are skipped (their weights are zero)
@@ -202,6 +206,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
             }
             const float mx = fmaxf(mx0, mx1);
             tmem_wait_st();
+            PH(1);
             m_true = fmaxf(m_true, mx);
             const bool rebase = mx > m_used && (m_used == -INFINITY || (mx - m_used) * c2 > rebase_limit<BF16>());
             float alpha = 1.f;
@@ -221,6 +226,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
                     tmem_st32(o_addr + c, r);
                 }
             }
+            PH(2);
             // pass 2: weights (hidden scores give exact zeros), their rounding and its residual, the normaliser
             const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
             const uint64_t m_pair = f2_pack(m_safe, m_safe), c2_pair = f2_pack(c2, c2);
@@ -261,12 +267,15 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
             float sum0, sum1;
             f2_unpack(sum, sum0, sum1);
             l += sum0 + sum1;
+            PH(3);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&sh.p_ready);
+            PH(4);
             ++iter;
         }
         if (iter > 0 && ok) ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 31);
+        PH(0);
         if (ok) {
             // tensor-memory loads are warp-collective: every lane takes part, only the stores are per row
             T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] +
@@ -302,6 +311,8 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
                 p.logsum[si] = l > 0.f ? log2f(l) + (m_used - m_true) * c2 : 0.f;
             }
         }
+        PH(7);
+        if (threadIdx.x == 0) PH_FLUSH(0);
     }
     tc_fence_before();
     __syncthreads();
@@ -714,5 +725,7 @@ cudaError_t launch_na_pipeline_backward(const AttnParams& p, bool bf16, int whic
     return bf16 ? backward_t<true, true>(p, st) : backward_t<true, false>(p, st);
 }
 
+
+KFA_PHASE_EXPORT(kfa_debug_phases_na)
 
 }  // namespace kfa

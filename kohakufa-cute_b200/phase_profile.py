@@ -13,6 +13,10 @@ Phases (index = position in the printed list):
   forward, MMA issuer                        : 0 wait for V, 1 wait for P, 2 issue P.V, 3 wait for K, 4 issue Q.K^T, 5 loop
   backward, consumer warpgroups              : 0 wait for the score tile, 1 tensor-memory loads, 2 P arithmetic,
                                                3 stores + hand-over, 4 set-up of the unit, 5 loop, 6 wait for dP, 7 dS arithmetic
+  neighbourhood forward, softmax warps       : 0 wait for the score tile (and the last product), 1 first pass (hide,
+                                               maximum), 2 re-base, 3 second pass (weights), 4 hand-over, 5 window
+                                               mask of the next tile, 6 start-up (barriers, window boxes, tile
+                                               bitmap), 7 epilogue
   backward, MMA issuers                      : 0 wait for the consumers, 1 issue gradient products, 2 wait for operands,
                                                3 issue score products, 4 loop, 5 further waits
 """
@@ -34,6 +38,7 @@ SLOTS = {
     "kfa_debug_phases_bwd": {0: "dQ       consumers wg 0", 1: "dQ       consumers wg 1", 2: "dQ       MMA issuer S",
                              3: "dQ       MMA issuer dP/dQ", 8: "dK/dV    consumers wg 0", 9: "dK/dV    consumers wg 1",
                              10: "dK/dV    MMA issuer"},
+    "kfa_debug_phases_na": {0: "neighbourhood forward softmax"},
 }
 
 
