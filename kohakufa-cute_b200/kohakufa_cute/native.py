@@ -168,12 +168,48 @@ def _blocks_shape(q, k, mask):
     )
 
 
+def tensor_core_head_dim(D):
+    """Channels the tensor-memory kernels run a head of ``D`` channels with: multiples of 8 up to 128 as they
+    are, other sizes padded with zero channels to the next multiple of 8 (up to 128) or to 256 / 384 / 512."""
+    if D <= 128:
+        return (D + 7) // 8 * 8
+    return 256 if D <= 256 else (384 if D <= 384 else 512)
+
+
+def _for_tensor_cores(tensors):
+    """The operands in a form the tensor-memory kernels address (the reference serves odd head sizes and
+    unaligned or channel-strided operands inside its MMA kernels with predicated loads, kernels.py:480-551;
+    here the tiled loads want 16-byte rows): zero channels appended up to ``tensor_core_head_dim`` - they add
+    nothing to either product, and the matching output channels are dropped again - and dense copies of operands
+    whose rows are not 16-byte addressable.  Returns the tensors unchanged when nothing has to be done."""
+    D = tensors[0].shape[-1]
+    target = tensor_core_head_dim(D)
+    if target == D and all(_rows_16_byte_addressable(t) for t in tensors):
+        return tensors, D
+    if target != D:
+        return [torch.nn.functional.pad(t, (0, target - D)) for t in tensors], D
+    return [t if _rows_16_byte_addressable(t) else t.contiguous() for t in tensors], D
+
+
+def _like(original, result):
+    """``result`` (possibly with extra channels) copied into a tensor laid out like ``original``, as the
+    reference allocates its outputs (native.cpp:295,348)."""
+    out = torch.empty_like(original)
+    out.copy_(result[..., : original.shape[-1]])
+    return out
+
+
 def forward(q, k, v, mask, scale, causal, statistics=True):
     """(out, maximum, logsum, blocks) - mirrors the reference extension's ``forward`` (native.cpp:1034).
     With ``statistics=False`` (a forward pass nobody will differentiate) the two row statistics are neither
     allocated nor written and come back as ``None``."""
     lib = library()
     q, k, v = _plain(q), _plain(k), _plain(v)
+    originals = (q, k, v)
+    (q, k, v), _ = _for_tensor_cores([q, k, v])
+    if any(a is not b for a, b in zip((q, k, v), originals)):
+        out, maximum, logsum, blocks = forward(q, k, v, mask, scale, causal, statistics)
+        return _like(originals[0], out), maximum, logsum, blocks
     with torch.cuda.device(q.device):
         out = torch.empty_like(q)
         maximum = torch.empty(q.shape[:-1], device=q.device, dtype=torch.float32) if statistics else None
@@ -277,10 +313,11 @@ def backward(q, k, v, mask, maximum, logsum, dout, blocks, out, scale, causal):
     """(dq, dk, dv) - mirrors the reference extension's ``backward`` (native.cpp:1038)."""
     lib = library()
     q, k, v, dout, out = _plain(q), _plain(k), _plain(v), _plain(dout), _plain(out)
-    if not _rows_16_byte_addressable(dout):
-        # expanded (stride-0), channel-strided or misaligned output gradients: the tensor-memory
-        # kernels address rows through TMA, so give them a dense copy
-        dout = dout.contiguous()
+    originals = (q, k, v)
+    (q, k, v, dout, out), _ = _for_tensor_cores([q, k, v, dout, out])
+    if any(a is not b for a, b in zip((q, k, v), originals)):
+        grads = backward(q, k, v, mask, maximum, logsum, dout, blocks, out, scale, causal)
+        return tuple(_like(o, g) for o, g in zip(originals, grads))
     with torch.cuda.device(q.device):
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         rq, rk = describe(q), describe(k)

@@ -190,6 +190,37 @@ def test_general_head_dims(shape, dtype):
     check_against_oracle(actual, q, k, v, dout, None, causal, None)
 
 
+def test_odd_head_dims_and_unaligned_rows_reach_the_tensor_core_kernels():
+    """Head sizes that are not multiples of 8 are padded with zero channels by the host layer, operands whose rows
+    are not 16-byte addressable are copied densely; either way the tensor-memory kernels do the work (the launch
+    statistics show which kernels ran) and the outputs keep the layout of their inputs."""
+    def launched(run):
+        before = native().launch_stats()
+        result = run()
+        after = native().launch_stats()
+        return result, {name: after[name] - before.get(name, 0) for name in after if after[name] != before.get(name, 0)}
+
+    for D, family in ((17, "pipeline"), (1, "pipeline"), (129, "wide"), (257, "wide")):
+        q, k, v, dout = make_inputs(1, 2, 1, 150, 200, D, torch.bfloat16, seed=300 + D)
+        actual, ran = launched(lambda: run_attention(api().attention, q, k, v, dout, causal=True))
+        assert any(name.startswith(family) for name in ran), (D, ran)
+        assert not any(name.startswith("general") for name in ran), (D, ran)
+        check_against_oracle(actual, q, k, v, dout, None, True, None)
+        assert all(a.shape == b.shape and a.stride() == b.stride() for a, b in zip(actual, (q, q, k, v)))
+    # rows that start at odd addresses: a channel offset of one element into a wider buffer
+    q, k, v, dout = make_inputs(1, 2, 2, 130, 130, 64, torch.float16, seed=333)
+    views = []
+    for t in (q, k, v):
+        big = torch.full((*t.shape[:-1], t.shape[-1] + 3), float("nan"), device=t.device, dtype=t.dtype)
+        big[..., 1:65] = t
+        views.append(big[..., 1:65])
+    actual, ran = launched(lambda: run_attention(api().attention, *views, dout, causal=False))
+    assert any(name.startswith("pipeline") for name in ran) and not any(name.startswith("general") for name in ran), ran
+    check_against_oracle(actual, q, k, v, dout, None, False, None)
+    # outputs are laid out like empty_like of their inputs (dense here: the views have gaps between rows)
+    assert actual[0].stride() == torch.empty_like(views[0]).stride() and actual[2].stride() == torch.empty_like(views[1]).stride()
+
+
 PADDED_HEAD_SHAPES = [
     # B, Hq, Hkv, Sq, Sk, D, causal: head dims that are multiples of 8 run on the tensor-memory pipeline as 64 or
     # 128 channels (the loads zero-fill the rest, the stores drop it)
