@@ -4,7 +4,7 @@
 // FP16/BF16, causal and/or boolean masks, grouped-query heads.
 //
 // One CTA owns 256 query rows of one (batch, query head) as two 128-row tiles and walks
-// the 128-key tiles they can see.  Warp roles (320 threads):
+// the 128-key tiles they can see.  Warp roles (384 threads):
 //   warps 0-3  softmax of query tile 0   (thread i <-> TMEM lane i <-> query row i)
 //   warps 4-7  softmax of query tile 1
 //   warp  8    issues every tcgen05.mma (one elected lane), owns the TMEM allocation
@@ -12,8 +12,11 @@
 //              that registers can be moved from it to the softmax warpgroups)
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 columns each.  The 16-bit
 // probabilities overwrite the first 64 columns of their score tile and feed the second
-// product straight from tensor memory.  While one tile's softmax runs, the tensor core
-// works on the other tile, and K/V tiles are shared by both.
+// product straight from tensor memory; they are handed over in two halves of 64 keys, so
+// the first half of P*V runs while the second half of the exponentials is formed.  While
+// one tile's softmax runs, the tensor core works on the other tile, and K/V tiles are
+// shared by both.  Block-wise callers (one block of a longer key sequence per call) get
+// the tile folded into a running FP32 state instead of a normalised output.
 //
 // Arithmetic (reference behaviour: src/kohakufa_cute/blackwell_pipeline.py:141-209,
 // 423-439 and kernels.py:1286-1333 of the reference project): scores are used unscaled,
