@@ -603,16 +603,21 @@ __global__ void __launch_bounds__(256, 1) wide_scores(const __grid_constant__ Wi
 }
 
 // ------------------------------------------------------------------- backward: gradient products
+constexpr int kGradStages = 2;  // two CTAs share an SM: one's start-up and epilogue run under the other's loads and products
+constexpr int kHalfChunkBytes = 64 * 128;  // 64 rows x 64 elements of a 16-bit type
+
 struct GradShared {
-    uint64_t full[2];
-    uint64_t empty[2];
+    uint64_t full[kGradStages];
+    uint64_t empty[kGradStages];
     uint64_t done;
     uint32_t tmem_base;
     int abort_word;
 };
 
 struct GradMaps {
-    CUtensorMap ds, p, k, q, g;  // the two stored matrices, K, Q and dO
+    CUtensorMap ds;              // dS_low, boxes of 64 keys x 128 queries (dQ: the matrix is the K-major A operand)
+    CUtensorMap ds64, p64;       // the two stored matrices, boxes of 64 keys x 64 queries (dK, dV: MN-major A)
+    CUtensorMap k64, q64, g64;   // K, Q and dO, boxes of 64 channels x 64 rows
 };
 
 // One launch forms all three gradients; the block index selects the product:
@@ -622,21 +627,23 @@ struct GradMaps {
 // (first `n_dq` blocks dQ, then `n_kv` blocks dK, then `n_kv` blocks dV; inside a product heavy causal
 // tiles of all heads come first, so the launch ends on light dV tiles.)  A CTA owns 128 output rows and
 // one half of the channels.  192 threads: warps 0-3 epilogue (thread <-> output row), warp 4 MMA issuer, warp 5
-// loader.  A stage holds one 128 x 128 block of the matrix (2 chunks) and 128 rows x D/2 channels
-// of the other operand.
+// loader.  A stage holds HALF of a unit's contraction range: 64 keys (dQ) or 64 queries (dK, dV) of the matrix
+// block (16 KB) and the same 64 rows x D/2 channels of the other operand; four such stages keep three loads in
+// flight while the fourth is consumed (with whole units per stage only one 96 KB load was in flight, and the
+// launch ran at a third of the rate at which shared memory can be filled).
 template <bool BF16>
-__global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ GradMaps maps, AttnParams p, unsigned n_dq,
+__global__ void __launch_bounds__(192, 2) wide_grad(const __grid_constant__ GradMaps maps, AttnParams p, unsigned n_dq,
                                                     unsigned n_kv) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int which = blockIdx.x < n_dq ? 0 : (blockIdx.x < n_dq + n_kv ? 1 : 2);
     const unsigned local = blockIdx.x - (which == 0 ? 0u : (which == 1 ? n_dq : n_dq + n_kv));
     const bool KV = which != 0;
-    const CUtensorMap* map_a = which == 2 ? &maps.p : &maps.ds;
-    const CUtensorMap* map_b = which == 0 ? &maps.k : (which == 1 ? &maps.q : &maps.g);
+    const CUtensorMap* map_a = which == 0 ? &maps.ds : (which == 1 ? &maps.ds64 : &maps.p64);
+    const CUtensorMap* map_b = which == 0 ? &maps.k64 : (which == 1 ? &maps.q64 : &maps.g64);
     const int hc = p.D >> 7;
-    const int stage_bytes = (2 + hc) * kChunkBytes;
-    GradShared& sh = *reinterpret_cast<GradShared*>(smem + 2 * stage_bytes);
+    const int stage_bytes = kChunkBytes + hc * kHalfChunkBytes;
+    GradShared& sh = *reinterpret_cast<GradShared*>(smem + kGradStages * stage_bytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = local & 1;
@@ -663,7 +670,7 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Grad
 
     if (threadIdx.x == 0) {
         sh.abort_word = *reinterpret_cast<volatile int*>(p.abort_flag) != 0 ? 90 : 0;  // 90: an earlier CTA gave up
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kGradStages; ++i) {
             mbar_init(&sh.full[i], 1);
             mbar_init(&sh.empty[i], 1);
         }
@@ -687,41 +694,48 @@ __global__ void __launch_bounds__(192, 1) wide_grad(const __grid_constant__ Grad
             tma_prefetch_desc(map_a);
             tma_prefetch_desc(map_b);
             bool ok = true;
-            for (int u = 0; u < units && ok; ++u) {
+            for (int v = 0; v < 2 * units && ok; ++v) {
+                const int u = v >> 1, sub = v & 1;  // unit and half of its contraction range
                 const int g = u / per_pass, i = first + u % per_pass;
-                const int s = u & 1;
-                if (u >= 2) ok = mbar_wait(&sh.empty[s], ((u >> 1) - 1) & 1, abort_word, 50);
+                const int s = v % kGradStages, round = v / kGradStages;
+                if (round > 0) ok = mbar_wait(&sh.empty[s], (round - 1) & 1, abort_word, 50);
                 if (!ok) break;
                 uint8_t* dst = smem + s * stage_bytes;
                 mbar_expect_tx(&sh.full[s], stage_bytes);
                 const int hq = KV ? head * p.group + g : head;
-                const int q_row = KV ? i * kTile : owner0, k_col = KV ? owner0 : i * kTile;
-                for (int c = 0; c < 2; ++c)
-                    tma_load_4d(dst + c * kChunkBytes, map_a, &sh.full[s], k_col + c * 64, q_row, hq, b);
-                // the other operand: K rows of the key tile (dQ), Q / dO rows of the query tile (dK / dV)
-                const int b_row = i * kTile, b_head = KV ? hq : head / p.group;
+                if (KV) {
+                    // 64 queries of the streamed tile x the owner's 128 keys, as two boxes of 64 keys
+                    for (int c = 0; c < 2; ++c)
+                        tma_load_4d(dst + c * kHalfChunkBytes, map_a, &sh.full[s], owner0 + c * 64, i * kTile + sub * 64,
+                                    hq, b);
+                } else {
+                    // the owner's 128 queries x 64 keys of the streamed tile
+                    tma_load_4d(dst, map_a, &sh.full[s], i * kTile + sub * 64, owner0, hq, b);
+                }
+                // the other operand: the same 64 rows of K (dQ) or of Q / dO (dK / dV), this CTA's channels
+                const int b_row = i * kTile + sub * 64, b_head = KV ? hq : head / p.group;
                 for (int c = 0; c < hc; ++c)
-                    tma_load_4d(dst + (2 + c) * kChunkBytes, map_b, &sh.full[s], (half * hc + c) * 64, b_row, b_head,
-                                b);
+                    tma_load_4d(dst + kChunkBytes + c * kHalfChunkBytes, map_b, &sh.full[s], (half * hc + c) * 64, b_row,
+                                b_head, b);
             }
         }
     } else if (warp == 4) {
         if (units > 0 && elect_one()) {
             const uint32_t idesc = umma_idesc(kTile, 64 * hc, BF16 ? 1 : 0, KV, true);
             const uint32_t base = smem_u32(smem);
-            const uint64_t a_desc = KV ? umma_desc_sw128(base, kChunkBytes, 1024) : umma_desc_sw128(base, 16, 1024);
-            const uint64_t b_desc = umma_desc_sw128(base + 2 * kChunkBytes, kChunkBytes, 1024);
+            const uint64_t a_desc = KV ? umma_desc_sw128(base, kHalfChunkBytes, 1024) : umma_desc_sw128(base, 16, 1024);
+            const uint64_t b_desc = umma_desc_sw128(base + kChunkBytes, kHalfChunkBytes, 1024);
             bool ok = true;
-            for (int u = 0; u < units && ok; ++u) {
-                const int s = u & 1;
-                ok = mbar_wait(&sh.full[s], (u >> 1) & 1, abort_word, 51);
+            for (int v = 0; v < 2 * units && ok; ++v) {
+                const int s = v % kGradStages;
+                ok = mbar_wait(&sh.full[s], (v / kGradStages) & 1, abort_word, 51);
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
-                for (int kk = 0; kk < kTile / 16; ++kk) {
-                    const uint32_t a_off = KV ? kk * 2048 : (kk / 4) * kChunkBytes + (kk % 4) * 32;
+                for (int kk = 0; kk < 4; ++kk) {  // 64 contraction rows per stage
+                    const uint32_t a_off = KV ? kk * 2048 : kk * 32;
                     umma_ss(tmem, umma_desc_advance(a_desc, s * stage_bytes + a_off),
-                            umma_desc_advance(b_desc, s * stage_bytes + kk * 2048), idesc, u > 0 || kk > 0);
+                            umma_desc_advance(b_desc, s * stage_bytes + kk * 2048), idesc, v > 0 || kk > 0);
                 }
                 umma_commit(&sh.empty[s]);
             }
@@ -831,7 +845,7 @@ __global__ void __launch_bounds__(256) wide_delta(AttnParams p) {
 
 // ------------------------------------------------------------------------------------ host side
 int smem_scores(int D) { return (D / 64 + kRing) * kChunkBytes + 1024 + 256; }
-int smem_grad(int D) { return 2 * (2 + D / 128) * kChunkBytes + 1024 + 256; }
+int smem_grad(int D) { return kGradStages * (kChunkBytes + (D / 128) * kHalfChunkBytes) + 1024 + 256; }
 
 bool wide_common(const AttnParams& p) {
     if (p.D != 256 && p.D != 384 && p.D != 512) return false;
@@ -845,9 +859,9 @@ CUtensorMapDataType map_type(bool bf16) {
     return bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
 }
 
-bool encode_stored(CUtensorMap* map, const void* ptr, bool bf16, const AttnParams& p, int64_t pitch) {
+bool encode_stored(CUtensorMap* map, const void* ptr, bool bf16, const AttnParams& p, int64_t pitch, int box_rows = kTile) {
     const int64_t strides[4] = {(int64_t)p.Hq * p.Sq * pitch, (int64_t)p.Sq * pitch, pitch, 1};
-    return encode_bhsd_map(map, ptr, map_type(bf16), p.Sk, p.Sq, p.Hq, p.B, strides, 64, kTile);
+    return encode_bhsd_map(map, ptr, map_type(bf16), p.Sk, p.Sq, p.Hq, p.B, strides, 64, box_rows);
 }
 
 template <typename K>
@@ -897,10 +911,11 @@ cudaError_t grad_t(const AttnParams& p, const Stored& stored, cudaStream_t st) {
     GradMaps maps;
     const CUtensorMapDataType dt = map_type(BF16);
     const bool ok = encode_stored(&maps.ds, stored.ds_low, BF16, p, stored.pitch) &&
-                    encode_stored(&maps.p, stored.p_low, BF16, p, stored.pitch) &&
-                    encode_bhsd_map(&maps.k, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, kTile) &&
-                    encode_bhsd_map(&maps.q, p.q, dt, p.D, p.Sq, p.Hq, p.B, p.qs, 64, kTile) &&
-                    encode_bhsd_map(&maps.g, p.dout, dt, p.D, p.Sq, p.Hq, p.B, p.gs, 64, kTile);
+                    encode_stored(&maps.ds64, stored.ds_low, BF16, p, stored.pitch, 64) &&
+                    encode_stored(&maps.p64, stored.p_low, BF16, p, stored.pitch, 64) &&
+                    encode_bhsd_map(&maps.k64, p.k, dt, p.D, p.Sk, p.Hkv, p.B, p.ks, 64, 64) &&
+                    encode_bhsd_map(&maps.q64, p.q, dt, p.D, p.Sq, p.Hq, p.B, p.qs, 64, 64) &&
+                    encode_bhsd_map(&maps.g64, p.dout, dt, p.D, p.Sq, p.Hq, p.B, p.gs, 64, 64);
     if (!ok) return cudaErrorInvalidValue;
     const int64_t n_dq = (int64_t)((p.Sq + kTile - 1) / kTile) * p.B * p.Hq * 2;
     const int64_t n_kv = (int64_t)((p.Sk + kTile - 1) / kTile) * p.B * p.Hkv * 2;
