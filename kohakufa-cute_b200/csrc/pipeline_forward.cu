@@ -337,6 +337,7 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_forward(const __grid_con
                 for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(r[i]);
             }
             tmem_wait_ld();
+            tmem_loaded(s);
             PH(1);
             const int key0 = j * kTileK;
             // leading columns of this tile that pass the sequence-end and causal bounds for this row

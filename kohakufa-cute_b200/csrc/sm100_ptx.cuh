@@ -138,6 +138,19 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Pins values that a tensor-memory load delivered behind the wait for that load: the registers are outputs of the load
+// instruction as far as the compiler knows, so without this nothing keeps it from scheduling their first use between
+// the load and the wait.  Expands to no instruction.
+template <int N>
+__device__ __forceinline__ void tmem_loaded(float (&v)[N]) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) asm volatile("" : "+f"(v[i]));
+}
+template <int N>
+__device__ __forceinline__ void tmem_loaded(uint32_t (&v)[N]) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) asm volatile("" : "+r"(v[i]));
+}
 
 // Arrives on `bar` once every tcgen05 operation issued so far by this thread
 // has completed.

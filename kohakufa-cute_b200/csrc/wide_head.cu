@@ -78,20 +78,20 @@ struct FwdShared {
     uint64_t q_full;
     uint64_t full[kRing];
     uint64_t empty[kRing];
-    uint64_t s_ready[2];  // per score buffer
+    uint64_t s_ready;
     uint64_t p_ready;
-    uint64_t pv_done;     // one phase per key tile: its P*V has completed (the output accumulator is quiescent)
+    uint64_t pvb_done;
     uint32_t tmem_base;
     int abort_word;
 };
 
-// maps.a = Q, maps.b = K, maps.c = V.  256 threads: warps 0-3 softmax (thread <-> query row), warp 4 the MMA
-// issuer (one elected lane), warps 5 and 7 loaders, warp 6 idle.  Tensor memory: two score buffers S0 (column 0)
-// and S1 (column 128) and O[:, half] (column 256).  The scores of key tile n+1 are formed into the other buffer
-// while the softmax works on tile n, so the softmax of consecutive tiles runs back to back and the tensor core
-// is not idle during it; P_low overwrites the first 64 columns of its own score buffer and feeds P*V from there,
-// one 64-channel V chunk per instruction (the chunks of a tile need not sit in consecutive ring slots then).
-// The loaders stream in the order the issuer consumes: K of the first tile, then K of tile n+1 before V of tile n.
+// maps.a = Q, maps.b = K, maps.c = V.  256 threads: warps 0-3 softmax (thread <-> query row),
+// warps 4 and 6 MMA issuers, warps 5 and 7 loaders.  A tcgen05.mma holds its issuing thread for about a
+// hundred cycles whatever its size, and a 512-channel score tile needs 32 of them, so the scores are
+// formed by TWO issuers into two partial accumulators: issuer 0 contracts the even 64-channel chunks
+// into S_a (column 0), issuer 1 the odd ones into S_b (column 128); the softmax adds the two.  Each
+// issuer then forms its share of the output channels of O[:, half] (column 256) from P_low, which
+// overwrites the first 64 columns of S_a.
 template <bool BF16>
 __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ WideMaps maps, AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -122,10 +122,9 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
             mbar_init(&sh.full[i], 1);
             mbar_init(&sh.empty[i], 1);
         }
-        mbar_init(&sh.s_ready[0], 1);
-        mbar_init(&sh.s_ready[1], 1);
+        mbar_init(&sh.s_ready, 2);  // both issuers
         mbar_init(&sh.p_ready, kTile);
-        mbar_init(&sh.pv_done, 1);
+        mbar_init(&sh.pvb_done, 1);
         mbar_fence_init();
     }
     if (warp == 4) {
@@ -137,11 +136,6 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
     tc_fence_after();
     const uint32_t tmem = sh.tmem_base;
     volatile int* abort_word = &sh.abort_word;
-    // first key tile at or after j that the mask table does not mark hidden (n_tiles: none)
-    auto next_visible = [&](int j) {
-        while (j < n_tiles && key_tile_state(p, b, h, q0, j) == 0) ++j;
-        return j;
-    };
 
     if (sh.abort_word != 0) {
         // an earlier CTA gave up: skip straight to the tear-down
@@ -161,85 +155,83 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
             }
             int pos = 0;
             bool ok = true;
-            // one ring position per 16 KB box; `which` 0: K chunk i of tile j, 1: V chunk i of this CTA's half
-            auto box = [&](int which, int j, int i) {
-                if ((pos & 1) == me) {
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (key_tile_state(p, b, h, q0, j) == 0) continue;
+                // the K chunks of the tile, then the V chunks of this CTA's channel half
+                for (int i = 0; i < chunks + hc && ok; ++i, ++pos) {
+                    if ((pos & 1) != me) continue;
                     const int slot = pos % kRing, round = pos / kRing;
                     if (round > 0) ok = mbar_wait(&sh.empty[slot], (round - 1) & 1, abort_word, 10);
-                    if (ok) {
-                        mbar_expect_tx(&sh.full[slot], kChunkBytes);
-                        if (which == 0)
-                            tma_load_4d(sRing + slot * kChunkBytes, &maps.b, &sh.full[slot], i * 64, j * kTile, kvh, b);
-                        else
-                            tma_load_4d(sRing + slot * kChunkBytes, &maps.c, &sh.full[slot], (half * hc + i) * 64,
-                                        j * kTile, kvh, b);
-                    }
+                    if (!ok) break;
+                    mbar_expect_tx(&sh.full[slot], kChunkBytes);
+                    if (i < chunks)
+                        tma_load_4d(sRing + slot * kChunkBytes, &maps.b, &sh.full[slot], i * 64, j * kTile, kvh, b);
+                    else
+                        tma_load_4d(sRing + slot * kChunkBytes, &maps.c, &sh.full[slot],
+                                    (half * hc + i - chunks) * 64, j * kTile, kvh, b);
                 }
-                ++pos;
-            };
-            int j = next_visible(0);
-            for (int i = 0; i < chunks && ok && j < n_tiles; ++i) box(0, j, i);
-            while (j < n_tiles && ok) {
-                const int jn = next_visible(j + 1);
-                for (int i = 0; i < chunks && ok && jn < n_tiles; ++i) box(0, jn, i);
-                for (int i = 0; i < hc && ok; ++i) box(1, j, i);
-                j = jn;
             }
         }
-    } else if (warp == 4) {
-        // ------------------------------------------------------------ MMA issuer
+    } else if (warp == 4 || warp == 6) {
+        // ----------------------------------------------------------- MMA issuers
         if (elect_one()) {
+            const int who = warp == 4 ? 0 : 1;
             const uint32_t idesc_s =
                 umma_idesc(kTile, kTile, BF16 ? 1 : 0, false, false) | (p.scale < 0.f ? kUmmaNegateA : 0u);
-            constexpr uint32_t idesc_o = umma_idesc(kTile, 64, BF16 ? 1 : 0, false, true);
+            // output channels of this CTA are split between the issuers by V chunk
+            const int ha = (hc + 1) / 2;
+            const int v_first = who == 0 ? 0 : ha, v_count = who == 0 ? ha : hc - ha;
+            const uint32_t idesc_o = umma_idesc(kTile, 64 * v_count, BF16 ? 1 : 0, false, true);
             const uint64_t q_desc = umma_desc_sw128(smem_u32(sQ), 16, 1024);
             const uint64_t k_desc = umma_desc_sw128(smem_u32(sRing), 16, 1024);
+            // the V chunks of one tile sit in consecutive slots: one instruction spans an issuer's share
             const uint64_t v_desc = umma_desc_sw128(smem_u32(sRing), kChunkBytes, 1024);
             bool ok = mbar_wait(&sh.q_full, 0, abort_word, 20);
-            int pos = 0;
-            // scores of one key tile into buffer `buf`: one ring position per 64-channel chunk of K
-            auto scores = [&](int buf) {
+            int pos = 0, iter = 0;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (key_tile_state(p, b, h, q0, j) == 0) continue;
+                // S_a also holds P_low of the previous tile, which issuer 1's product is still reading
+                if (who == 0 && iter > 0) ok = mbar_wait(&sh.pvb_done, (iter - 1) & 1, abort_word, 24);
                 for (int c = 0; c < chunks && ok; ++c, ++pos) {
+                    if ((c & 1) != who) continue;
                     const int slot = pos % kRing;
                     ok = mbar_wait(&sh.full[slot], (pos / kRing) & 1, abort_word, 21);
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
-                        umma_ss(tmem + buf * 128, umma_desc_advance(q_desc, c * kChunkBytes + kk * 32),
-                                umma_desc_advance(k_desc, slot * kChunkBytes + kk * 32), idesc_s, c > 0 || kk > 0);
+                        umma_ss(tmem + who * 128, umma_desc_advance(q_desc, c * kChunkBytes + kk * 32),
+                                umma_desc_advance(k_desc, slot * kChunkBytes + kk * 32), idesc_s, c > who || kk > 0);
                     umma_commit(&sh.empty[slot]);
                 }
-                if (ok) umma_commit(&sh.s_ready[buf]);
-            };
-            int j = next_visible(0), iter = 0;
-            if (ok && j < n_tiles) scores(0);
-            while (j < n_tiles && ok) {
-                const int jn = next_visible(j + 1);
-                if (jn < n_tiles) scores((iter + 1) & 1);  // runs while the softmax works on this tile
+                if (!ok) break;
+                umma_commit(&sh.s_ready);
+                const int s0 = (pos + v_first) % kRing;
+                for (int i = 0; i < v_count && ok; ++i)
+                    ok = mbar_wait(&sh.full[(pos + v_first + i) % kRing], ((pos + v_first + i) / kRing) & 1, abort_word,
+                                   22);
                 if (ok) ok = mbar_wait(&sh.p_ready, iter & 1, abort_word, 23);
-                for (int i = 0; i < hc && ok; ++i, ++pos) {
-                    const int slot = pos % kRing;
-                    ok = mbar_wait(&sh.full[slot], (pos / kRing) & 1, abort_word, 22);
-                    if (!ok) break;
-                    tc_fence_after();
+                if (!ok) break;
+                tc_fence_after();
+                if (v_count > 0) {
 #pragma unroll
                     for (int kk = 0; kk < kTile / 16; ++kk)
-                        umma_ts(tmem + 256 + i * 64, tmem + (iter & 1) * 128 + kk * 8,
-                                umma_desc_advance(v_desc, slot * kChunkBytes + kk * 2048), idesc_o, iter > 0 || kk > 0);
-                    umma_commit(&sh.empty[slot]);
+                        umma_ts(tmem + 256 + v_first * 64, tmem + kk * 8,
+                                umma_desc_advance(v_desc, s0 * kChunkBytes + kk * 2048), idesc_o, iter > 0 || kk > 0);
                 }
-                if (ok) umma_commit(&sh.pv_done);
-                j = jn;
+                for (int i = 0; i < v_count; ++i) umma_commit(&sh.empty[(pos + v_first + i) % kRing]);
+                if (who == 1) umma_commit(&sh.pvb_done);
+                pos += hc;
                 ++iter;
             }
+            if (ok) umma_commit(&sh.s_ready);  // completion of the last product
         }
     } else if (warp < 4) {
         // --------------------------------------------------------------- softmax
         using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
         const int row = q0 + warp * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-        const uint32_t o_addr = lane_base + 256;
+        const uint32_t s_addr = lane_base, o_addr = lane_base + 256;
         const int width = 64 * hc;  // output channels of this CTA
         const float c2 = fabsf(p.scale) * kLog2e;
         const uint64_t c2_pair = f2_pack(c2, c2);
@@ -253,19 +245,19 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int state = key_tile_state(p, b, h, q0, j);
             if (state == 0) continue;
-            const uint32_t s_addr = lane_base + (iter & 1) * 128;  // this tile's score buffer
-            ok = mbar_wait(&sh.s_ready[iter & 1], (iter >> 1) & 1, abort_word, 30);
+            ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 30);
             if (!ok) break;
             tc_fence_after();
             float s[kTile];
 #pragma unroll
             for (int c = 0; c < kTile; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(s_addr + c, r);
+                uint32_t ra[32], rb[32];
+                tmem_ld32(s_addr + c, ra);
+                tmem_ld32(s_addr + 128 + c, rb);
+                tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(r[i]);
+                for (int i = 0; i < 32; ++i) s[c + i] = __uint_as_float(ra[i]) + __uint_as_float(rb[i]);
             }
-            tmem_wait_ld();
             const int key0 = j * kTile;
             int lim = p.Sk - key0;
             if (p.causal) lim = min(lim, row + p.causal_shift - key0 + 1);
@@ -295,12 +287,8 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
                 l *= alpha;
                 m_used = mx;
             }
-            // rare: the previous tile's P*V must have completed before the accumulator is touched (the scores of
-            // this tile were formed before it was issued)
+            // s_ready of this tile was committed after the previous product, so O is quiescent here
             if (iter > 0 && __any_sync(0xffffffffu, rebase)) {
-                ok = mbar_wait(&sh.pv_done, (iter - 1) & 1, abort_word, 32);
-                if (!ok) break;
-                tc_fence_after();
                 for (int c = 0; c < width; c += 32) {
                     uint32_t r[32];
                     tmem_ld32(o_addr + c, r);
@@ -355,7 +343,7 @@ __global__ void __launch_bounds__(256, 1) wide_forward(const __grid_constant__ W
             }
         }
         if (iter > 0) {
-            if (ok) ok = mbar_wait(&sh.pv_done, (iter - 1) & 1, abort_word, 31);
+            if (ok) ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 31);
             if (ok) {
                 tc_fence_after();
                 const float den = l > 0.f ? l : 1.f;
