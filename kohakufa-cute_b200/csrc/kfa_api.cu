@@ -345,6 +345,11 @@ int geometry(kfa::AttnParams& p, const int64_t* spatial, int nd, const int64_t* 
 namespace kfa {
 void note_failure(int code, const char* message) { fail(code, "%s", message); }
 void count_launches(const char* name, int n) { count_kernel(name, (uint64_t)n); }
+// One launch sequence under the per-kernel event timing and launch statistics of this file (for entry points that
+// live in other translation units).
+cudaError_t timed_launch(const char* name, cudaStream_t st, cudaError_t (*launch)(void*), void* context) {
+    return timed(name, st, [&] { return launch(context); });
+}
 }  // namespace kfa
 
 extern "C" {
