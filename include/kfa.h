@@ -172,6 +172,20 @@ KFA_API int kfa_merge_partial(kfa_tensor* acc_out, kfa_tensor* acc_maximum, kfa_
                       const kfa_tensor* part_logsum, float scale, void* stream);
 
 /*
+ * Forward for token-by-token decoding against a key/value cache: at most 8 query rows per K/V head (query positions
+ * x grouped-query heads), 64 or 128 channels, at least 512 keys, no mask, not causal.  The reference serves short query
+ * sequences with its split forward (split_forward.py:125-245); here the call is a CUDA-core kernel bound by the HBM
+ * time of K and V (the keys of a head are split over CTAs, partial results merged with the (maximum, sum)
+ * arithmetic of split_forward.py:219-245) instead of one 128-row tensor-core tile per head.  Results and statistics
+ * follow kfa_forward's contract; maximum/logsum may both be NULL.  Other operands: KFA_INVALID_ARGUMENT.
+ *   workspace: kfa_forward_decode_workspace_bytes(q, k) bytes, 16-byte aligned
+ */
+KFA_API size_t kfa_forward_decode_workspace_bytes(const kfa_tensor* q, const kfa_tensor* k);
+KFA_API int kfa_forward_decode(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, kfa_tensor* out,
+                       kfa_tensor* maximum, kfa_tensor* logsum, void* workspace, size_t workspace_bytes, float scale,
+                       void* stream);
+
+/*
  * Block-wise forms for callers that hold only one block of a longer sequence at a time (ring context
  * parallelism; no counterpart in the reference, whose split forward keeps FP32 partial outputs with (maximum, sum)
  * pairs and merges them afterwards: split_forward.py:125-245).  Nothing is rounded to the 16-bit type between

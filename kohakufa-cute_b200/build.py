@@ -19,7 +19,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "kohakufa_cute")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(OUT_DIR, "libkfa.so")
-SOURCES = ["kfa_api.cu", "general_kernels.cu", "neighborhood_kernels.cu", "pipeline_forward.cu",
+SOURCES = ["kfa_api.cu", "general_kernels.cu", "neighborhood_kernels.cu", "pipeline_forward.cu", "decode_forward.cu",
            "pipeline_backward.cu", "wide_head.cu", "na_pipeline.cu", "tensor_map.cu", "static_scratch.cu", "wait_probe.cu", "center_keys_cluster.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-Wno-deprecated-gpu-targets"]

@@ -642,6 +642,43 @@ int kfa_forward(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, c
     return 0;
 }
 
+size_t kfa_forward_decode_workspace_bytes(const kfa_tensor* q, const kfa_tensor* k) {
+    if (!q || !k || q->ndim != 4 || k->ndim != 4) return 0;
+    return kfa::decode_forward_workspace_bytes(q->sizes[0], q->sizes[1], k->sizes[1], q->sizes[2], k->sizes[2], q->sizes[3]);
+}
+
+int kfa_forward_decode(const kfa_tensor* q, const kfa_tensor* k, const kfa_tensor* v, kfa_tensor* out,
+                       kfa_tensor* maximum, kfa_tensor* logsum, void* workspace, size_t workspace_bytes, float scale,
+                       void* stream) {
+    if (int e = check_device_ok()) return e;
+    if (int e = check_qkv(q, k, v)) return e;
+    kfa::AttnParams p;
+    if (int e = fill_common(p, q, k, v, nullptr, scale, 0, static_cast<cudaStream_t>(stream))) return e;
+    if (int e = check_like(out, q, "out")) return e;
+    const bool keep_statistics = maximum != nullptr || logsum != nullptr;
+    if (keep_statistics && (!contiguous3(maximum, p.B, p.Hq, p.Sq) || !contiguous3(logsum, p.B, p.Hq, p.Sq)))
+        return fail(KFA_INVALID_ARGUMENT, "maximum/logsum must be contiguous float32 [B,Hq,Sq] (or both NULL)");
+    p.out = out->data;
+    copy4(p.os, out->strides);
+    p.maximum = keep_statistics ? static_cast<float*>(maximum->data) : nullptr;
+    p.logsum = keep_statistics ? static_cast<float*>(logsum->data) : nullptr;
+    if (!kfa::decode_forward_supported(p))
+        return fail(KFA_INVALID_ARGUMENT,
+                    "decode forward serves at most 8 query rows per K/V head (positions x grouped heads), 64 or 128 "
+                    "channels, at least 512 keys, no mask, not causal, a non-zero scale, 8-byte addressable rows");
+    if (!workspace || workspace_bytes < kfa_forward_decode_workspace_bytes(q, k) ||
+        reinterpret_cast<uintptr_t>(workspace) % 16 != 0)
+        return fail(KFA_INVALID_ARGUMENT, "decode forward workspace too small or not 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int launches = 0;
+    cudaError_t ce = timed("decode_forward", st, [&] {
+        return kfa::launch_decode_forward(p, q->dtype == KFA_BF16, workspace, &launches, st);
+    });
+    if (ce != cudaSuccess) return cuda_fail(ce, "decode forward launch");
+    if (launches > 1) count_kernel("decode_forward", (uint64_t)(launches - 1));
+    return 0;
+}
+
 int kfa_pack_mask(const kfa_tensor* mask, kfa_tensor* blocks, void* stream) {
     if (!mask || !mask->data || mask->dtype != KFA_BOOL || mask->ndim != 4)
         return fail(KFA_INVALID_ARGUMENT, "pack_mask requires a boolean mask expanded to [B,Hq,Sq,Sk]");

@@ -30,6 +30,12 @@ cudaError_t launch_finish_running(void* out, float* maximum, float* logsum, cons
                                   const float* run_sum, bool bf16, int B, int H, int S, int D, const int64_t* as,
                                   const int64_t* os, cudaStream_t st);
 
+// Forward for at most eight query rows per K/V head against a long key sequence (decoding): CUDA-core kernels bound
+// by the HBM time of K and V.  `workspace` holds the partial results of the key ranges.
+bool decode_forward_supported(const AttnParams& p);
+size_t decode_forward_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t Sq, int64_t Sk, int64_t D);
+cudaError_t launch_decode_forward(const AttnParams& p, bool bf16, void* workspace, int* launches, cudaStream_t st);
+
 cudaError_t launch_neighborhood_forward(const AttnParams& p, bool bf16, cudaStream_t st);
 cudaError_t launch_neighborhood_backward(const AttnParams& p, bool bf16, int which, cudaStream_t st);
 

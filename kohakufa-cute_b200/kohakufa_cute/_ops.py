@@ -106,8 +106,10 @@ center_keys_op.register_autograd(_center_backward, setup_context=lambda ctx, inp
 
 
 def _eager_forward(q, k, v, mask, scale, causal, statistics):
-    """Forward through the C ABI: split over the keys when a short query sequence would otherwise leave most
-    of the GPU idle, one launch otherwise."""
+    """Forward through the C ABI: the decoding kernel for a few query rows against a long cache, split over the
+    keys when a short query sequence would otherwise leave most of the GPU idle, one launch otherwise."""
+    if native.decode_served(q, k, v, mask, causal):
+        return native.forward_decode(q, k, v, scale, statistics)
     splits = native.split_plan(q, k, causal)
     if splits:
         return native.forward_split(q, k, v, mask, scale, splits, statistics)

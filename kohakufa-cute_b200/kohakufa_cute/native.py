@@ -52,6 +52,8 @@ SIGNATURES = {
     "kfa_backward_workspace_bytes": (ctypes.c_size_t, [_TP, _TP]),
     "kfa_backward": (ctypes.c_int, [_TP] * 12 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float, ctypes.c_int,
                                                  ctypes.c_void_p]),
+    "kfa_forward_decode_workspace_bytes": (ctypes.c_size_t, [_TP, _TP]),
+    "kfa_forward_decode": (ctypes.c_int, [_TP] * 6 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float, ctypes.c_void_p]),
     "kfa_forward_running": (ctypes.c_int, [_TP] * 8 + [ctypes.c_float, ctypes.c_int, ctypes.c_void_p]),
     "kfa_finish_running": (ctypes.c_int, [_TP] * 6 + [ctypes.c_void_p]),
     "kfa_backward_partial": (ctypes.c_int, [_TP] * 12 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float, ctypes.c_int,
@@ -220,6 +222,35 @@ def forward(q, k, v, mask, scale, causal, statistics=True):
             blocks = torch.empty(_blocks_shape(q, k, mask), device=q.device, dtype=torch.int32)
         records = [describe(t) for t in (q, k, v, mask, out, maximum, logsum, blocks if mask is not None else None)]
         _check(lib.kfa_forward(*[_ref(r) for r in records], float(scale), int(bool(causal)), _stream(q.device)))
+    return out, maximum, logsum, blocks
+
+
+def decode_served(q, k, v, mask, causal):
+    """Whether ``forward_decode`` serves the call: a few query rows per K/V head (positions x grouped heads <= 8)
+    against at least 512 keys, 64 or 128 channels, no mask, not causal, 8-byte addressable rows."""
+    if mask is not None or causal or q.shape[-1] not in (64, 128) or k.shape[2] < 512:
+        return False
+    if q.shape[2] * (q.shape[1] // k.shape[1]) > 8:
+        return False
+    return all(t.stride(-1) == 1 and t.data_ptr() % 8 == 0 and all(s % 4 == 0 for s in t.stride()[:-1]) for t in (q, k, v))
+
+
+def forward_decode(q, k, v, scale, statistics=True):
+    """(out, maximum, logsum, blocks) through ``kfa_forward_decode``: the decoding shapes of ``decode_served``
+    on CUDA-core kernels bound by the HBM time of K and V."""
+    lib = library()
+    q, k, v = _plain(q), _plain(k), _plain(v)
+    with torch.cuda.device(q.device):
+        out = torch.empty_like(q)
+        maximum = torch.empty(q.shape[:-1], device=q.device, dtype=torch.float32) if statistics else None
+        logsum = torch.empty_like(maximum) if statistics else None
+        rq, rk = describe(q), describe(k)
+        need = lib.kfa_forward_decode_workspace_bytes(_ref(rq), _ref(rk))
+        workspace = torch.empty(need, device=q.device, dtype=torch.uint8)
+        records = [rq, rk, describe(v), describe(out), describe(maximum), describe(logsum)]
+        _check(lib.kfa_forward_decode(*[_ref(r) for r in records], ctypes.c_void_p(workspace.data_ptr()), need,
+                                      float(scale), _stream(q.device)))
+        blocks = torch.empty((1, 1, 1, 1), device=q.device, dtype=torch.int32)
     return out, maximum, logsum, blocks
 
 
