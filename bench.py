@@ -555,7 +555,7 @@ def sdpa_comparator(device, steps=20):
 
 def decode_probe(device, steps=200):
     """One query row per head against 32768 keys (B=1, Hq=32, Hkv=8, D=128, bf16), forward only and without
-    gradients: the split-over-keys forward.  Memory-bound: reported as time and as K/V bytes per second."""
+    gradients: the decoding kernel.  Memory-bound: reported as time and as K/V bytes per second, eager and as a CUDA graph."""
     import kohakufa_cute
 
     try:
@@ -575,10 +575,24 @@ def decode_probe(device, steps=200):
                 kohakufa_cute.attention(*sets[i % 4])
             e.record()
             torch.cuda.synchronize()
-        ms = b.elapsed_time(e) / steps
+            ms = b.elapsed_time(e) / steps
+            # the same four calls as one CUDA graph: the device time without the host's launch cost
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                kept = [kohakufa_cute.attention(*inputs) for inputs in sets]
+            for _ in range(3):
+                graph.replay()
+            b.record()
+            for _ in range(steps // 4):
+                graph.replay()
+            e.record()
+            torch.cuda.synchronize()
+            graph_ms = b.elapsed_time(e) / (steps // 4 * 4)
+            del kept
         kv_bytes = 2 * 8 * 32768 * 128 * 2
-        return {"workload": "decode (B1 Hq32 Hkv8 Sq1 Sk32768 D128, forward only, no gradients, eager)",
-                "ms_per_call": ms, "kv_gbs": kv_bytes / (ms * 1e-3) / 1e9}
+        return {"workload": "decode (B1 Hq32 Hkv8 Sq1 Sk32768 D128, forward only, no gradients)",
+                "ms_per_call": ms, "kv_gbs": kv_bytes / (ms * 1e-3) / 1e9, "launch": "eager",
+                "graph_ms_per_call": graph_ms, "graph_kv_gbs": kv_bytes / (graph_ms * 1e-3) / 1e9}
     except Exception as error:
         return {"workload": "decode", "error": f"{type(error).__name__}: {error}"[:200]}
 
