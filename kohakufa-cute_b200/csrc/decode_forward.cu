@@ -264,9 +264,12 @@ __global__ void __launch_bounds__(128) decode_merge(DecodeParams p, int D, T* ou
     const float inv = total > 0.f ? 1.f / total : 0.f;
     const int d = threadIdx.x;
     if (d < D) {
-        float acc = 0.f;
-#pragma unroll 8
-        for (int i = 0; i < p.splits; ++i) acc = fmaf(p.part_out[((int64_t)i * all_rows + row) * D + d], weight[i], acc);
+        float part[kMaxSplits], acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < kMaxSplits; ++i)  // every load is issued before the first is used
+            part[i] = i < p.splits ? p.part_out[((int64_t)i * all_rows + row) * D + d] : 0.f;
+#pragma unroll
+        for (int i = 0; i < kMaxSplits; ++i) acc = fmaf(part[i], i < p.splits ? weight[i] : 0.f, acc);
         out[(int64_t)b * o_b + (int64_t)hq * o_h + (int64_t)sq * o_s + d] = from_float<T>(acc * inv);
     }
     if (threadIdx.x == 0 && maximum) {
@@ -276,8 +279,10 @@ __global__ void __launch_bounds__(128) decode_merge(DecodeParams p, int D, T* ou
     }
 }
 
-int splits_for(int64_t units, int64_t Sk) {
-    // about four CTAs per SM over the whole call, at least 256 keys per CTA
+// Key ranges per (batch, K/V head): about four CTAs per SM over the whole call, at least 256 keys each (several
+// short CTAs per slot balance better than one wave of long ones: measured).
+int splits_for(int64_t units, int64_t Sk, int rows) {
+    (void)rows;
     int64_t want = (4 * 148 + units - 1) / units;
     const int64_t most = Sk / 256 > 0 ? Sk / 256 : 1;
     want = want < 1 ? 1 : (want > most ? most : want);
@@ -309,7 +314,7 @@ bool decode_forward_supported(const AttnParams& p) {
 size_t decode_forward_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t Sq, int64_t Sk, int64_t D) {
     if (Hkv <= 0) return 0;
     const int64_t rows = B * Hq * Sq;
-    const int splits = splits_for(B * Hkv, Sk);
+    const int splits = splits_for(B * Hkv, Sk, (int)(Sq * (Hq / Hkv)));
     return (size_t)(splits * rows * (D + 2)) * sizeof(float);
 }
 
@@ -330,7 +335,7 @@ cudaError_t launch_decode_forward(const AttnParams& p, bool bf16, void* workspac
     d.Sk = p.Sk;
     d.group = p.group;
     d.rows = p.Sq * p.group;
-    d.splits = splits_for((int64_t)p.B * p.Hkv, p.Sk);
+    d.splits = splits_for((int64_t)p.B * p.Hkv, p.Sk, d.rows);
     d.keys_per_split = ((p.Sk + d.splits - 1) / d.splits + 63) / 64 * 64;
     d.c2 = fabsf(p.scale) * kLog2e;
     d.sign = p.scale < 0.f ? -1.f : 1.f;
