@@ -687,7 +687,7 @@ cudaError_t launch_center_keys(const void* k, void* out, float* workspace, bool 
                                const int64_t* ks, const int64_t* os, cudaStream_t st, int* launches) {
     // one launch over thread-block clusters when a head's slab fits in shared memory and the device can
     // co-schedule the cluster; a failed cluster launch (a partition that cannot) falls through as well
-    if (center_keys_cluster_supported(k, out, S, D, ks, os) && center_keys_cluster_schedulable(bf16, S, D)) {
+    if (center_keys_cluster_supported(k, out, B, H, S, D, ks, os) && center_keys_cluster_schedulable(bf16, S, D)) {
         if (launch_center_keys_cluster(k, out, bf16, B, H, S, D, ks, os, st) == cudaSuccess) {
             if (launches) *launches = 1;
             return cudaSuccess;

@@ -13,7 +13,8 @@ cudaError_t launch_general_backward(const AttnParams& p, bool bf16, int which, c
 // partial-sum path that uses `workspace`.
 cudaError_t launch_center_keys(const void* k, void* out, float* workspace, bool bf16, int B, int H, int S, int D,
                                const int64_t* ks, const int64_t* os, cudaStream_t st, int* launches = nullptr);
-bool center_keys_cluster_supported(const void* k, const void* out, int S, int D, const int64_t* ks, const int64_t* os);
+bool center_keys_cluster_supported(const void* k, const void* out, int B, int H, int S, int D, const int64_t* ks,
+                                   const int64_t* os);
 // False when this device cannot co-schedule the cluster the one-launch kernel needs (queried once per device).
 bool center_keys_cluster_schedulable(bool bf16, int S, int D);
 cudaError_t launch_center_keys_cluster(const void* k, void* out, bool bf16, int B, int H, int S, int D,

@@ -476,11 +476,13 @@ def test_center_keys_kernel_matches_the_contract(dtype):
     assert float(back.float().sum(-2).abs().max()) < 0.1
 
 
-@pytest.mark.parametrize("shape", ((4, 8, 4096, 128), (1, 3, 1000, 64), (2, 2, 65, 512), (1, 2, 777, 256)))
+@pytest.mark.parametrize("shape", ((4, 8, 4096, 128), (1, 3, 1000, 64), (2, 2, 65, 512), (1, 2, 777, 256),
+                                   (6, 8, 4096, 128), (1, 2, 40001, 64)))
 @pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
 def test_center_keys_cluster_kernel(shape, dtype):
-    """Heads whose slab fits in shared memory are centred by one launch over thread-block clusters: same
-    values as the FP32 definition (to one rounding of the mean), bitwise reproducible, any 16-byte row layout."""
+    """Tensors of up to 40 MB (any sequence length: the rows are read a second time from L2) and larger ones whose
+    slab of S/8 rows fits in shared memory (the 50 MB case) are centred by one launch over thread-block clusters:
+    same values as the FP32 definition (to one rounding of the mean), bitwise reproducible, any 16-byte row layout."""
     B, H, S, D = shape
     gen = torch.Generator().manual_seed(S + D)
     k = (torch.randn(B, H, S, D, generator=gen) + 3 * torch.randn(B, H, 1, D, generator=gen)).to(dtype).cuda()
@@ -493,7 +495,10 @@ def test_center_keys_cluster_kernel(shape, dtype):
     torch.testing.assert_close(native().center_keys(k), got, atol=0, rtol=0)
     strided = strided_like_projection(k)
     torch.testing.assert_close(native().center_keys(strided), got, atol=0, rtol=0)
-    assert float(got.float().sum(2).abs().max()) < 0.02 * S ** 0.5 * float(want.float().abs().max()) + 0.1
+    # the column sums that are left: those of the definition (rounding k - mean to 16 bits is biased when the keys
+    # sit on a coarse grid around a large offset), up to the elements whose rounding the last bit of the mean flips
+    left = (got.float().sum(2) - want.float().sum(2)).abs().max()
+    assert float(left) < 0.02 * S ** 0.5 * float(want.float().abs().max()) + 0.1
 
 
 def _launched(fn):

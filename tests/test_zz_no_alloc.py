@@ -3,8 +3,8 @@
 Some hosts of the library cannot allocate device memory while they run (a server with a fixed
 arena, a C plugin host that owns only the tensors it passes in), so this entry point takes its
 scratch from a fixed array inside the library.  The test calls it through the C ABI several times in a
-row on shapes that really go through that array (fewer than 64 rows, a channel count or a sequence
-slab the one-launch cluster kernel does not take), a many-split shape followed by few-split ones so that
+row on shapes that really go through that array (fewer than 64 rows, a channel count or a tensor
+size the one-launch cluster kernel does not take), a many-split shape followed by few-split ones so that
 the later calls meet the earlier calls' leftovers, and requires bit-identical results to
 ``kfa_center_keys`` (same kernels, same summation order).  It also covers a shape the cluster kernel
 serves, for which the array is not touched at all.  The file sorts last so that a run stopping at the
@@ -19,7 +19,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 # (shape, dtype, kernels launched): three = the partial sums and means went through the static array
-CASES = (((1, 1, 8192, 128), torch.bfloat16, 3),   # 32 sequence splits; slab of 1024 rows x 128 channels too large
+CASES = (((1, 1, 172032, 128), torch.bfloat16, 3),  # 32 sequence splits; 44 MB: too large for either cluster kernel
          ((1, 2, 50, 64), torch.float16, 3),       # one split, fewer than 64 rows
          ((2, 3, 700, 96), torch.bfloat16, 3),     # 5 splits, 96 channels
          ((2, 3, 700, 128), torch.bfloat16, 1))    # cluster kernel: no scratch at all
