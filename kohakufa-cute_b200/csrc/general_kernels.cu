@@ -172,9 +172,8 @@ __global__ void __launch_bounds__(128) output_delta(AttnParams p) {
     const int64_t row_id = (int64_t)blockIdx.x * 128 + threadIdx.x;
     const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
     if (row_id >= rows) return;
-    const int r = (int)(row_id % p.Sq);
-    const int h = (int)((row_id / p.Sq) % p.Hq);
-    const int b = (int)(row_id / ((int64_t)p.Sq * p.Hq));
+    int r, h, b;
+    split_row(row_id, p.Sq, p.Hq, r, h, b);
     const T* o = reinterpret_cast<const T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] + (int64_t)r * p.os[2];
     const T* g = reinterpret_cast<const T*>(p.dout) + (int64_t)b * p.gs[0] + (int64_t)h * p.gs[1] + (int64_t)r * p.gs[2];
     float sum = 0.f;
@@ -528,7 +527,8 @@ __global__ void __launch_bounds__(128) merge_partial(float* acc, float* am, floa
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (row >= rows) return;
-    const int s = (int)(row % S), h = (int)((row / S) % H), b = (int)(row / ((int64_t)S * H));
+    int s, h, b;
+    split_row(row, S, H, s, h, b);
     const float m0 = am[row], l0 = al[row], m1 = pm[row], l1 = pl[row];
     const float m = fmaxf(m0, m1);
     float w0 = 0.f, w1 = 0.f;
@@ -558,7 +558,8 @@ __global__ void __launch_bounds__(128) finish_running(T* out, float* maximum, fl
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (row >= rows) return;
-    const int s = (int)(row % S), h = (int)((row / S) % H), b = (int)(row / ((int64_t)S * H));
+    int s, h, b;
+    split_row(row, S, H, s, h, b);
     const float l = run_sum[row];
     const float inv = l > 0.f ? 1.f / l : 0.f;
     const float* arow = acc + (int64_t)b * a_b + (int64_t)h * a_h + (int64_t)s * a_s;
@@ -580,7 +581,8 @@ __global__ void __launch_bounds__(128) merge_splits(T* out, float* maximum, floa
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (row >= rows) return;
-    const int s = (int)(row % S), h = (int)((row / S) % H), b = (int)(row / ((int64_t)S * H));
+    int s, h, b;
+    split_row(row, S, H, s, h, b);
     float m = -INFINITY;
     for (int i = 0; i < splits; ++i) m = fmaxf(m, pm[(int64_t)i * rows + row]);
     float total = 0.f;

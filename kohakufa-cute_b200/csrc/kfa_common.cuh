@@ -66,6 +66,21 @@ struct AttnParams {
     int* abort_flag;  // device memory: set by the first CTA whose bounded wait gives up; later CTAs skip their work
 };
 
+// (batch, head, position) of row `row_id` of a [B, H, S] row space.  32-bit divisions when the index fits: a 64-bit
+// division costs more instructions than the loads of a row in the row-wise kernels.
+__device__ __forceinline__ void split_row(int64_t row_id, int S, int H, int& s, int& h, int& b) {
+    if (row_id <= 0xffffffffll) {
+        const uint32_t head = (uint32_t)row_id / (uint32_t)S;
+        s = (int)((uint32_t)row_id - head * (uint32_t)S);
+        b = (int)(head / (uint32_t)H);
+        h = (int)(head - (uint32_t)b * (uint32_t)H);
+    } else {
+        s = (int)(row_id % S);
+        h = (int)((row_id / S) % H);
+        b = (int)(row_id / ((int64_t)S * H));
+    }
+}
+
 template <typename T>
 __device__ __forceinline__ float to_float(T x);
 template <>

@@ -57,7 +57,8 @@ __global__ void __launch_bounds__(128) na_forward(AttnParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row_id = (int64_t)blockIdx.x * 4 + warp;
     if (row_id >= (int64_t)p.B * p.Hq * p.Sq) return;
-    const int row = (int)(row_id % p.Sq), h = (int)((row_id / p.Sq) % p.Hq), b = (int)(row_id / ((int64_t)p.Sq * p.Hq));
+    int row, h, b;
+    split_row(row_id, p.Sq, p.Hq, row, h, b);
     const T* qrow = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.qs[0] + (int64_t)h * p.qs[1] + (int64_t)row * p.qs[2];
     const T* kb = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.ks[0] + (int64_t)h * p.ks[1];
     const T* vb = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.vs[0] + (int64_t)h * p.vs[1];
@@ -117,7 +118,8 @@ __global__ void __launch_bounds__(128) na_backward_q(AttnParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row_id = (int64_t)blockIdx.x * 4 + warp;
     if (row_id >= (int64_t)p.B * p.Hq * p.Sq) return;
-    const int row = (int)(row_id % p.Sq), h = (int)((row_id / p.Sq) % p.Hq), b = (int)(row_id / ((int64_t)p.Sq * p.Hq));
+    int row, h, b;
+    split_row(row_id, p.Sq, p.Hq, row, h, b);
     const T* qrow = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.qs[0] + (int64_t)h * p.qs[1] + (int64_t)row * p.qs[2];
     const T* grow = reinterpret_cast<const T*>(p.dout) + (int64_t)b * p.gs[0] + (int64_t)h * p.gs[1] + (int64_t)row * p.gs[2];
     const T* kb = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.ks[0] + (int64_t)h * p.ks[1];
@@ -182,7 +184,8 @@ __global__ void __launch_bounds__(128) na_backward_kv(AttnParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t key_id = (int64_t)blockIdx.x * 4 + warp;
     if (key_id >= (int64_t)p.B * p.Hq * p.Sk) return;
-    const int key = (int)(key_id % p.Sk), h = (int)((key_id / p.Sk) % p.Hq), b = (int)(key_id / ((int64_t)p.Sk * p.Hq));
+    int key, h, b;
+    split_row(key_id, p.Sk, p.Hq, key, h, b);
     const T* krow = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.ks[0] + (int64_t)h * p.ks[1] + (int64_t)key * p.ks[2];
     const T* vrow = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.vs[0] + (int64_t)h * p.vs[1] + (int64_t)key * p.vs[2];
     const T* qb = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.qs[0] + (int64_t)h * p.qs[1];

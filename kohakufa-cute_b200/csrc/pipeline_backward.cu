@@ -159,31 +159,45 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_backward_q(const __grid_
 }
 
 // delta[row] = sum_d O * dO with coalesced 16-byte loads: D/8 threads per row (D = 64 or 128 covers the
-// head's p.D channels; the threads beyond them add zero).
+// head's p.D channels; the threads beyond them add zero), kDeltaBatch rows per thread so that each thread has
+// 2 x kDeltaBatch independent loads in flight before the first use.
+constexpr int kDeltaBatch = 2;
+
 template <typename T, int D>
 __global__ void __launch_bounds__(256) output_delta_rows(AttnParams p) {
     constexpr int kLanes = D / 8, kRows = 256 / kLanes;
     const int sub = threadIdx.x % kLanes;
-    const int64_t row_id = (int64_t)blockIdx.x * kRows + threadIdx.x / kLanes;
+    const int64_t first = (int64_t)blockIdx.x * (kRows * kDeltaBatch) + threadIdx.x / kLanes;
     const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
-    float sum = 0.f;
-    if (row_id < rows && sub * 8 < p.D) {
-        const int r = (int)(row_id % p.Sq);
-        const int h = (int)((row_id / p.Sq) % p.Hq);
-        const int b = (int)(row_id / ((int64_t)p.Sq * p.Hq));
-        const T* o = reinterpret_cast<const T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] +
-                     (int64_t)r * p.os[2] + sub * 8;
-        const T* g = reinterpret_cast<const T*>(p.dout) + (int64_t)b * p.gs[0] + (int64_t)h * p.gs[1] +
-                     (int64_t)r * p.gs[2] + sub * 8;
-        const uint4 ov = *reinterpret_cast<const uint4*>(o), gv = *reinterpret_cast<const uint4*>(g);
-        const T* oe = reinterpret_cast<const T*>(&ov);
-        const T* ge = reinterpret_cast<const T*>(&gv);
+    const bool channels = sub * 8 < p.D;
+    uint4 ov[kDeltaBatch], gv[kDeltaBatch];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) sum = fmaf(to_float<T>(oe[e]), to_float<T>(ge[e]), sum);
+    for (int j = 0; j < kDeltaBatch; ++j) {
+        const int64_t row_id = first + j * kRows;
+        ov[j] = gv[j] = make_uint4(0, 0, 0, 0);
+        if (row_id < rows && channels) {
+            int r, h, b;
+            split_row(row_id, p.Sq, p.Hq, r, h, b);
+            const T* o = reinterpret_cast<const T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] +
+                         (int64_t)r * p.os[2] + sub * 8;
+            const T* g = reinterpret_cast<const T*>(p.dout) + (int64_t)b * p.gs[0] + (int64_t)h * p.gs[1] +
+                         (int64_t)r * p.gs[2] + sub * 8;
+            ov[j] = *reinterpret_cast<const uint4*>(o);
+            gv[j] = *reinterpret_cast<const uint4*>(g);
+        }
     }
 #pragma unroll
-    for (int o = kLanes / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (sub == 0 && row_id < rows) p.delta[row_id] = sum;
+    for (int j = 0; j < kDeltaBatch; ++j) {
+        const T* oe = reinterpret_cast<const T*>(&ov[j]);
+        const T* ge = reinterpret_cast<const T*>(&gv[j]);
+        float sum = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum = fmaf(to_float<T>(oe[e]), to_float<T>(ge[e]), sum);
+#pragma unroll
+        for (int o = kLanes / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const int64_t row_id = first + j * kRows;
+        if (sub == 0 && row_id < rows) p.delta[row_id] = sum;
+    }
 }
 
 std::atomic<int> g_configured{0};
@@ -257,11 +271,11 @@ cudaError_t launch_pipeline_backward(const AttnParams& p, bool bf16, int which, 
 cudaError_t launch_pipeline_delta(const AttnParams& p, bool bf16, cudaStream_t st) {
     const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
     if (p.D > 64) {
-        const unsigned grid = (unsigned)((rows + 15) / 16);
+        const unsigned grid = (unsigned)((rows + 16 * kDeltaBatch - 1) / (16 * kDeltaBatch));
         if (bf16) output_delta_rows<__nv_bfloat16, 128><<<grid, 256, 0, st>>>(p);
         else output_delta_rows<__half, 128><<<grid, 256, 0, st>>>(p);
     } else {
-        const unsigned grid = (unsigned)((rows + 31) / 32);
+        const unsigned grid = (unsigned)((rows + 32 * kDeltaBatch - 1) / (32 * kDeltaBatch));
         if (bf16) output_delta_rows<__nv_bfloat16, 64><<<grid, 256, 0, st>>>(p);
         else output_delta_rows<__half, 64><<<grid, 256, 0, st>>>(p);
     }

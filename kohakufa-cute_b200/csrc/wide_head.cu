@@ -826,9 +826,8 @@ __global__ void __launch_bounds__(256) wide_delta(AttnParams p) {
     const int64_t row_id = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
     if (row_id >= rows) return;
-    const int r = (int)(row_id % p.Sq);
-    const int h = (int)((row_id / p.Sq) % p.Hq);
-    const int b = (int)(row_id / ((int64_t)p.Sq * p.Hq));
+    int r, h, b;
+    split_row(row_id, p.Sq, p.Hq, r, h, b);
     const T* o = reinterpret_cast<const T*>(p.out) + (int64_t)b * p.os[0] + (int64_t)h * p.os[1] + (int64_t)r * p.os[2];
     const T* g = reinterpret_cast<const T*>(p.dout) + (int64_t)b * p.gs[0] + (int64_t)h * p.gs[1] + (int64_t)r * p.gs[2];
     float sum = 0.f;
