@@ -68,8 +68,8 @@ WORKLOADS = {
                             seed=5, grid=(16, 32, 32), window=(3, 7, 7), graph=True),
 }
 # short runs added to the headline line: (workload, steps, minimum seconds of timed region)
-OTHERS_SINGLE = (("wide_head", 20, 0.2), ("d128_4k", 20, 0.2), ("dit_masked", 3, 0.3), ("neighborhood_3d", 20, 0.2),
-                 ("neighborhood_2d", 20, 0.2))
+OTHERS_SINGLE = (("wide_head", 20, 0.2), ("wide_head_4k", 20, 0.2), ("d128_4k", 20, 0.2), ("d64_4k", 20, 0.2),
+                 ("dit_masked", 3, 0.3), ("neighborhood_3d", 20, 0.2), ("neighborhood_2d", 20, 0.2))
 OTHERS_MULTI = (("dit_ring", 2, 0.0), ("llm_ring_causal", 2, 0.0))
 
 # GEMMs of the seven algorithmic ones (S, PV forward; S, dP, dV, dK, dQ backward counted as 5) attributed to a
