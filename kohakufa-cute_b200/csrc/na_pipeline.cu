@@ -175,9 +175,10 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
         int iter = 0;
         bool ok = true;
         PH(6);
+        BoxCursor cursor = box_cursor(p, box);
         for (int j = next_tile(sh.bitmap, 0); j >= 0 && ok; j = next_tile(sh.bitmap, j + 1)) {
             uint32_t vis[4] = {0, 0, 0, 0};
-            if (row_ok) box_mask<4>(p, box, j * kTile, p.Sk, vis);
+            if (row_ok) box_mask_walk<4>(p, box, cursor, j * kTile, vis);
             PH(5);
             ok = mbar_wait(&sh.s_ready, iter & 1, abort_word, 30);
             if (!ok) break;
@@ -361,7 +362,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
     BwdShared& sh = *reinterpret_cast<BwdShared*>(sRing + kStages * 2 * kSubBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int owner_len = KV ? p.Sk : p.Sq, partner_len = KV ? p.Sq : p.Sk;
+    const int owner_len = KV ? p.Sk : p.Sq;
     const int nblk = (owner_len + kTile - 1) / kTile;
     const int blk = (int)(blockIdx.x % nblk);
     const int64_t bh = blockIdx.x / nblk;
@@ -480,6 +481,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
         const int tid = warp * 32 + lane;
         int n = 0;
         bool ok = true;
+        BoxCursor cursor = box_cursor(p, box);
         for (int j = next_tile(sh.bitmap, 0); j >= 0 && ok; j = next_tile(sh.bitmap, j + 1), ++n) {
             const int part0 = j * kSub;
             if (KV) {
@@ -501,7 +503,7 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
                 bar_sync(1, kTile);
             }
             uint32_t vis[2] = {0, 0};
-            if (row_ok) box_mask<2>(p, box, part0, partner_len, vis);
+            if (row_ok) box_mask_walk<2>(p, box, cursor, part0, vis);
             ok = mbar_wait(&sh.sdp_ready, n & 1, abort_word, 64);
             if (!ok) break;
             tc_fence_after();

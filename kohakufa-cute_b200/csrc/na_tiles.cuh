@@ -23,7 +23,7 @@ struct Box {
 };
 
 // Keys visible to query `token`.
-__device__ __forceinline__ Box query_box(const AttnParams& p, int token) {
+__host__ __device__ __forceinline__ Box query_box(const AttnParams& p, int token) {
     const int x = token % p.ext[2], t = token / p.ext[2], y = t % p.ext[1], z = t / p.ext[1];
     Box b;
     b.zlo = na_start(z, p.ext[0], p.win[0]);
@@ -36,7 +36,7 @@ __device__ __forceinline__ Box query_box(const AttnParams& p, int token) {
 }
 
 // Queries that see key `token`.
-__device__ __forceinline__ Box key_box(const AttnParams& p, int token) {
+__host__ __device__ __forceinline__ Box key_box(const AttnParams& p, int token) {
     const int x = token % p.ext[2], t = token / p.ext[2], y = t % p.ext[1], z = t / p.ext[1];
     Box b;
     na_inverse(z, p.ext[0], p.win[0], b.zlo, b.zhi);
@@ -71,7 +71,7 @@ __device__ __forceinline__ int next_tile(const uint32_t* bitmap, int j) {
 // `limit` is the length of the partner sequence.  The tile is walked grid row by grid row (two integer
 // divisions per call, none per row).
 template <int WORDS>
-__device__ __forceinline__ void box_mask(const AttnParams& p, const Box& b, int tok0, int limit, uint32_t (&m)[WORDS]) {
+__host__ __device__ __forceinline__ void box_mask(const AttnParams& p, const Box& b, int tok0, int limit, uint32_t (&m)[WORDS]) {
 #pragma unroll
     for (int w = 0; w < WORDS; ++w) m[w] = 0;
     const int ex = p.ext[2], ey = p.ext[1];
@@ -93,6 +93,65 @@ __device__ __forceinline__ void box_mask(const AttnParams& p, const Box& b, int 
             y = 0;
             ++z;
         }
+    }
+}
+
+// The same masks for a walk over tiles in increasing order (any tiles may be left out): the cursor stands on the first
+// grid row of the box that is not yet wholly behind the walk, so a call touches only the rows of the box that reach
+// into its tile (box_mask tests every grid row of the tile and divides twice per call).
+struct BoxCursor {
+    int next;  // token of (z, y, xlo), the start of the row's run; kDone when the box is used up
+    int z, y;
+};
+constexpr int kDone = 0x3fffffff;
+
+__host__ __device__ __forceinline__ BoxCursor box_cursor(const AttnParams& p, const Box& b) {
+    BoxCursor c;
+    c.z = b.zlo;
+    c.y = b.ylo;
+    const bool empty = b.zhi < b.zlo || b.yhi < b.ylo || b.xhi < b.xlo;
+    c.next = empty ? kDone : (b.zlo * p.ext[1] + b.ylo) * p.ext[2] + b.xlo;
+    return c;
+}
+
+__host__ __device__ __forceinline__ void box_cursor_advance(const AttnParams& p, const Box& b, BoxCursor& c) {
+    if (c.y < b.yhi) {
+        ++c.y;
+        c.next += p.ext[2];
+    } else if (c.z < b.zhi) {
+        ++c.z;
+        c.y = b.ylo;
+        c.next = (c.z * p.ext[1] + b.ylo) * p.ext[2] + b.xlo;
+    } else {
+        c.next = kDone;
+    }
+}
+
+// Bit c of the result (word c / 32) is set when partner token tok0 + c lies in the box.  tok0 must not decrease
+// from one call to the next with the same cursor.
+template <int WORDS>
+__host__ __device__ __forceinline__ void box_mask_walk(const AttnParams& p, const Box& b, BoxCursor& c, int tok0,
+                                                       uint32_t (&m)[WORDS]) {
+    static_assert(WORDS == 2 || WORDS == 4, "tiles of 64 or 128 partner tokens");
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) m[w] = 0;
+    const int len = b.xhi - b.xlo;  // run length - 1
+    const int end = tok0 + 32 * WORDS;
+    while (c.next + len < tok0) box_cursor_advance(p, b, c);
+    while (c.next < end) {
+        const int lo = (c.next > tok0 ? c.next : tok0) - tok0;
+        const int hi = (c.next + len < end ? c.next + len : end - 1) - tok0;
+#pragma unroll
+        for (int q = 0; q < WORDS / 2; ++q) {  // 64 bits at a time
+            const int a = lo - 64 * q > 0 ? lo - 64 * q : 0, e = hi - 64 * q < 63 ? hi - 64 * q : 63;
+            if (a <= e) {
+                const unsigned long long bits = (~0ull >> (63 - (e - a))) << a;
+                m[2 * q] |= static_cast<uint32_t>(bits);
+                m[2 * q + 1] |= static_cast<uint32_t>(bits >> 32);
+            }
+        }
+        if (c.next + len >= end) break;  // the run goes on in the next tile: the cursor stays on it
+        box_cursor_advance(p, b, c);
     }
 }
 
