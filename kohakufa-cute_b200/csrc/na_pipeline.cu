@@ -94,10 +94,8 @@ __global__ void __launch_bounds__(192, 2) na_tc_forward(const __grid_constant__ 
     const int row = q0 + warp * 32 + lane;
     const bool row_ok = warp < 4 && row < p.Sq;
     Box box = {0, -1, 0, -1, 0, -1};
-    if (row_ok) {
-        box = query_box(p, row);
-        mark_tiles(p, box, kTile, sh.bitmap);
-    }
+    if (row_ok) box = query_box(p, row);
+    if (warp < 4) mark_tiles_warp(p, box, row_ok, kTile, sh.bitmap);
     __syncthreads();
     const uint32_t tmem = sh.tmem_base;
     volatile int* abort_word = &sh.abort_word;
@@ -392,10 +390,8 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
     const int row = owner0 + warp * 32 + lane;
     const bool row_ok = warp < 4 && row < owner_len;
     Box box = {0, -1, 0, -1, 0, -1};
-    if (row_ok) {
-        box = KV ? key_box(p, row) : query_box(p, row);
-        mark_tiles(p, box, kSub, sh.bitmap);
-    }
+    if (row_ok) box = KV ? key_box(p, row) : query_box(p, row);
+    if (warp < 4) mark_tiles_warp(p, box, row_ok, kSub, sh.bitmap);
     __syncthreads();
     const uint32_t tmem = sh.tmem_base;
     volatile int* abort_word = &sh.abort_word;

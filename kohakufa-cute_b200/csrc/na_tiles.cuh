@@ -55,6 +55,34 @@ __device__ __forceinline__ void mark_tiles(const AttnParams& p, const Box& b, in
         }
 }
 
+// The same for a whole warp (every lane calls it; `valid` says whether the lane has a box).  The lanes of a warp are
+// consecutive tokens, so their boxes nearly always share the z and y ranges: the warp then marks the tiles of the
+// hull of its x ranges once, one (z, y) row per lane, instead of every lane marking every row (32 conflicting
+// shared-memory atomics per row).  The hull may mark a tile no lane sees: such a tile contributes nothing.
+__device__ __forceinline__ void mark_tiles_warp(const AttnParams& p, const Box& b, bool valid, int width,
+                                                uint32_t* bitmap) {
+    const unsigned full = 0xffffffffu;
+    const unsigned have = __ballot_sync(full, valid);
+    if (have == 0) return;
+    const int leader = __ffs(have) - 1, lane = threadIdx.x & 31;
+    const int zlo = __shfl_sync(full, b.zlo, leader), zhi = __shfl_sync(full, b.zhi, leader);
+    const int ylo = __shfl_sync(full, b.ylo, leader), yhi = __shfl_sync(full, b.yhi, leader);
+    const bool same = !valid || (b.zlo == zlo && b.zhi == zhi && b.ylo == ylo && b.yhi == yhi);
+    if (__all_sync(full, same)) {
+        const int xlo = __reduce_min_sync(full, valid ? b.xlo : 0x7fffffff);
+        const int xhi = __reduce_max_sync(full, valid ? b.xhi : -1);
+        const int ny = yhi - ylo + 1, rows = (zhi - zlo + 1) * ny;
+        for (int i = lane; i < rows; i += 32) {
+            const int z = zlo + i / ny, y = ylo + i % ny;
+            const int row0 = (z * p.ext[1] + y) * p.ext[2];
+            const int first = (row0 + xlo) / width, last = (row0 + xhi) / width;
+            for (int t = first; t <= last; ++t) atomicOr(&bitmap[t >> 5], 1u << (t & 31));
+        }
+    } else if (valid) {
+        mark_tiles(p, b, width, bitmap);
+    }
+}
+
 // First marked tile with index >= j, or -1.
 __device__ __forceinline__ int next_tile(const uint32_t* bitmap, int j) {
     int w = j >> 5;

@@ -20,7 +20,7 @@ ROOT = os.path.dirname(HERE)
 def test_mask_walk_matches_direct_masks_and_definition(tmp_path):
     exe = str(tmp_path / "na_mask_walk_check")
     build = subprocess.run(
-        ["nvcc", "-std=c++17", "-O2", "-Wno-deprecated-gpu-targets", "-I", os.path.join(ROOT, "kohakufa-cute_b200", "csrc"),
+        ["nvcc", "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-I", os.path.join(ROOT, "kohakufa-cute_b200", "csrc"),
          "-o", exe, os.path.join(HERE, "host_checks", "na_mask_walk_check.cu")],
         capture_output=True, text=True, timeout=600)
     assert build.returncode == 0, build.stderr[-2000:]
