@@ -185,8 +185,7 @@ __host__ __device__ __forceinline__ void box_mask_walk(const AttnParams& p, cons
 
 // -inf where bit `i` of `vis` is clear, the score itself where it is set.
 __device__ __forceinline__ uint32_t hide(uint32_t score_bits, uint32_t vis, int i) {
-    const uint32_t keep = static_cast<uint32_t>(static_cast<int32_t>(vis << (31 - i)) >> 31);
-    return (score_bits & keep) | (~keep & 0xff800000u);
+    return (vis & (1u << i)) != 0 ? score_bits : 0xff800000u;
 }
 
 }  // namespace na
