@@ -337,7 +337,7 @@ struct BwdShared {
     uint32_t tmem_base;
     int abort_word;
     uint32_t bitmap[kMapWords];
-    float stats[2][4][kSub];  // per streamed query: maximum, logsum, delta, t (key owners only)
+    float stats[2][4][kSub];  // per streamed query: maximum, logsum, delta + t (key owners only; the fourth row is unused)
 };
 
 struct BwdMaps {
@@ -493,8 +493,8 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
                 } else {
                     const int qi = part0 + tid - kSub;
                     const bool in = qi < p.Sq;
-                    stat[2 * kSub + tid - kSub] = in ? p.delta[stat0 + qi] : 0.f;
-                    stat[3 * kSub + tid - kSub] = in ? p.aux[stat0 + qi] : 0.f;
+                    // (dP - delta) - t is formed as dP - (delta + t): the sum is staged once per query
+                    stat[2 * kSub + tid - kSub] = in ? p.delta[stat0 + qi] + p.aux[stat0 + qi] : 0.f;
                 }
                 bar_sync(1, kTile);
             }
@@ -526,10 +526,9 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
                         const float2 mm = *reinterpret_cast<const float2*>(stat + half * 32 + c);
                         const float2 ll = *reinterpret_cast<const float2*>(stat + kSub + half * 32 + c);
                         const float2 dd = *reinterpret_cast<const float2*>(stat + 2 * kSub + half * 32 + c);
-                        const float2 tt = *reinterpret_cast<const float2*>(stat + 3 * kSub + half * 32 + c);
                         m2 = f2_pack(mm.x, mm.y);
                         ls2 = f2_pack(ll.x, ll.y);
-                        dl2 = f2_pack(dd.x + tt.x, dd.y + tt.y);  // (dP - delta) - t, both belong to the query
+                        dl2 = f2_pack(dd.x, dd.y);  // delta + t of the query
                     } else {
                         m2 = f2_pack(row_m, row_m);
                         ls2 = f2_pack(row_ls, row_ls);
