@@ -337,7 +337,7 @@ struct BwdShared {
     uint32_t tmem_base;
     int abort_word;
     uint32_t bitmap[kMapWords];
-    float stats[2][4][kSub];  // per streamed query: maximum, logsum, delta + t (key owners only; the fourth row is unused)
+    alignas(16) float stats[2][4][kSub];  // per streamed query: maximum, logsum, delta + t (key owners only; the fourth row is unused)
 };
 
 struct BwdMaps {
@@ -519,16 +519,19 @@ __global__ void __launch_bounds__(192, 2) na_tc_backward(const __grid_constant__
                 tmem_ld32(lane_base + half * 32, s);
                 tmem_ld32(lane_base + 64 + half * 32, dp);
                 tmem_wait_ld();
+                float4 mm4, ll4, dd4;  // key owners: the statistics of four streamed queries per 16-byte load
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
                     uint64_t m2, ls2, dl2;
                     if (KV) {
-                        const float2 mm = *reinterpret_cast<const float2*>(stat + half * 32 + c);
-                        const float2 ll = *reinterpret_cast<const float2*>(stat + kSub + half * 32 + c);
-                        const float2 dd = *reinterpret_cast<const float2*>(stat + 2 * kSub + half * 32 + c);
-                        m2 = f2_pack(mm.x, mm.y);
-                        ls2 = f2_pack(ll.x, ll.y);
-                        dl2 = f2_pack(dd.x, dd.y);  // delta + t of the query
+                        if ((c & 2) == 0) {
+                            mm4 = *reinterpret_cast<const float4*>(stat + half * 32 + c);
+                            ll4 = *reinterpret_cast<const float4*>(stat + kSub + half * 32 + c);
+                            dd4 = *reinterpret_cast<const float4*>(stat + 2 * kSub + half * 32 + c);
+                        }
+                        m2 = (c & 2) == 0 ? f2_pack(mm4.x, mm4.y) : f2_pack(mm4.z, mm4.w);
+                        ls2 = (c & 2) == 0 ? f2_pack(ll4.x, ll4.y) : f2_pack(ll4.z, ll4.w);
+                        dl2 = (c & 2) == 0 ? f2_pack(dd4.x, dd4.y) : f2_pack(dd4.z, dd4.w);  // delta + t of the query
                     } else {
                         m2 = f2_pack(row_m, row_m);
                         ls2 = f2_pack(row_ls, row_ls);
