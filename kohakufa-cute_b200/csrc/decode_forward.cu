@@ -281,8 +281,7 @@ __global__ void __launch_bounds__(128) decode_merge(DecodeParams p, int D, T* ou
 
 // Key ranges per (batch, K/V head): about four CTAs per SM over the whole call, at least 256 keys each (several
 // short CTAs per slot balance better than one wave of long ones: measured).
-int splits_for(int64_t units, int64_t Sk, int rows) {
-    (void)rows;
+int splits_for(int64_t units, int64_t Sk) {
     int64_t want = (4 * 148 + units - 1) / units;
     const int64_t most = Sk / 256 > 0 ? Sk / 256 : 1;
     want = want < 1 ? 1 : (want > most ? most : want);
@@ -314,7 +313,7 @@ bool decode_forward_supported(const AttnParams& p) {
 size_t decode_forward_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t Sq, int64_t Sk, int64_t D) {
     if (Hkv <= 0) return 0;
     const int64_t rows = B * Hq * Sq;
-    const int splits = splits_for(B * Hkv, Sk, (int)(Sq * (Hq / Hkv)));
+    const int splits = splits_for(B * Hkv, Sk);
     return (size_t)(splits * rows * (D + 2)) * sizeof(float);
 }
 
@@ -335,7 +334,7 @@ cudaError_t launch_decode_forward(const AttnParams& p, bool bf16, void* workspac
     d.Sk = p.Sk;
     d.group = p.group;
     d.rows = p.Sq * p.group;
-    d.splits = splits_for((int64_t)p.B * p.Hkv, p.Sk, d.rows);
+    d.splits = splits_for((int64_t)p.B * p.Hkv, p.Sk);
     d.keys_per_split = ((p.Sk + d.splits - 1) / d.splits + 63) / 64 * 64;
     d.c2 = fabsf(p.scale) * kLog2e;
     d.sign = p.scale < 0.f ? -1.f : 1.f;
