@@ -1,4 +1,4 @@
-"""Host logic of the multi-GPU layers, run as gloo ranks on the CPU (world size 2 and 3).
+"""Host logic of the multi-GPU layers, run as gloo ranks on the CPU (world size 2, 3 and 4).
 
 The CUDA kernels are replaced by CPU stand-ins built on the oracle, so these tests cover the
 sharding arithmetic, the ring schedule (who holds which block when, also under the causal zig-zag layout),
@@ -124,7 +124,8 @@ def _ring_worker(rank, world, port, masked, causal, result):
 
 
 @pytest.mark.parametrize("world,masked,causal", ((2, False, False), (2, True, False), (3, True, False),
-                                                 (2, False, True), (3, False, True), (3, True, True)))
+                                                 (2, False, True), (3, False, True), (3, True, True),
+                                                 (4, True, True)))
 def test_ring_schedule_and_merge_on_cpu_ranks(world, masked, causal):
     manager = mp.Manager()
     result = manager.dict()
